@@ -13,6 +13,11 @@ and fixed-size per-sequence state.
   ``ring_tokens`` positions (position p lives in cell p % ring_tokens): the
   window plus room for the longest step that continues a sequence
   (``max_continuation`` positions; by default one page more than the window).
+* A group whose need names ``pool`` = P also keeps one *cell* per block of P positions
+  (positions bP .. bP + P - 1; the mixer writes a block's cell in the step that brings the
+  block's last position): a second paged store whose "position" b is block b and which
+  never wraps.  Its ring then keeps max(window, P) positions, so that a block's positions
+  are still there when its last one arrives.
 * *State* is a fixed-size tensor per slot and schedule entry for mixers
   that carry a recurrent state instead of keys; it is zeroed when the slot
   is acquired.  (The attention mixer needs none.)
@@ -63,6 +68,8 @@ class KVNeed:
     value_dim: int = 0       # width of a value; 0: the same as a key
     # a value is (the leading part of) its key's cell: no pool of values is kept
     values_in_keys: bool = False
+    # P > 0: beside the positions, one key cell and one value cell per block of P positions
+    pool: int = 0
 
     @property
     def v_dim(self) -> int:
@@ -113,6 +120,35 @@ class PagePool:
             self._free.append(p)
 
 
+class BlockCells:
+    """One key cell and one value cell per block of ``block`` positions, for the layers of one
+    group: pages of ``page_tokens`` cells, a page table per slot, every block kept."""
+
+    def __init__(self, need: "KVNeed", n_entries: int, total_tokens: int, max_slots: int,
+                 max_seq_len: int, page_tokens: int, dtype: torch.dtype, device: torch.device):
+        self.block = need.pool
+        self.page_tokens = page_tokens
+        self.pages_per_seq = max(1, -(-(max_seq_len // self.block) // page_tokens))
+        # every sequence may hold one partly filled page of cells beside its share of the blocks
+        n_pages = -(-(total_tokens // self.block) // page_tokens) + max_slots
+        self.n_pages = min(n_pages, max_slots * self.pages_per_seq)
+        self.pool = PagePool(self.n_pages)
+        shape = (n_entries, self.n_pages, need.n_kv_heads, page_tokens)
+        self.k = torch.zeros(shape + (need.head_dim,), dtype=dtype, device=device)
+        self.v = torch.zeros(shape + (need.v_dim,), dtype=dtype, device=device)
+        self.table_host = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32)
+        self.table = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
+        self.pages: List[List[int]] = [[] for _ in range(max_slots)]
+        self.dirty = False
+
+    def pages_for(self, length: int) -> int:
+        """Pages of cells a sequence of ``length`` positions holds (whole blocks only)."""
+        return min(-(-(length // self.block) // self.page_tokens), self.pages_per_seq)
+
+    def bytes(self) -> int:
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
+
+
 class KVGroup:
     """Storage of the layers (schedule entries) that share one :class:`KVNeed`."""
 
@@ -123,13 +159,15 @@ class KVGroup:
         self.entries = list(entries)
         self.page_tokens = page_tokens
         full_pages = -(-max_seq_len // page_tokens)
+        # what a ring keeps behind a position: the window, and a whole block where blocks are pooled
+        self.keep = max(need.window, need.pool) if need.window > 0 else 0
         if need.window <= 0:
             ring_pages = full_pages
         elif max_continuation is None:
-            ring_pages = -(-need.window // page_tokens) + 1
+            ring_pages = -(-self.keep // page_tokens) + 1
         else:
             # a step of c positions writes c - 1 cells ahead of what its first row still sees
-            ring_pages = -(-(need.window + max(1, max_continuation) - 1) // page_tokens)
+            ring_pages = -(-(self.keep + max(1, max_continuation) - 1) // page_tokens)
         if ring_pages >= full_pages:
             self.ring_tokens = 0          # never wraps
             self.pages_per_seq = full_pages
@@ -148,6 +186,12 @@ class KVGroup:
         self.table = torch.zeros((max_slots, self.pages_per_seq), dtype=torch.int32, device=device)
         self.pages: List[List[int]] = [[] for _ in range(max_slots)]
         self.dirty = False
+        self.cells: Optional[BlockCells] = None
+        if need.pool > 0:
+            if need.window <= 0 or need.values_in_keys:
+                raise CacheError("pooled blocks go with a window and with values of their own")
+            self.cells = BlockCells(need, len(entries), n_pages * page_tokens, max_slots,
+                                    max_seq_len, page_tokens, dtype, device)
 
     def pages_for(self, length: int) -> int:
         """Pages a sequence of ``length`` positions holds in this group."""
@@ -160,12 +204,12 @@ class KVGroup:
         also add whatever does not wrap around the ring."""
         if self.ring_tokens == 0:
             return 1 << 30
-        room = self.ring_tokens - self.need.window + 1
+        room = self.ring_tokens - self.keep + 1
         return room if start is None else max(self.ring_tokens - start, room)
 
     def bytes(self) -> int:
         held = self.k.numel() + (0 if self.v is self.k else self.v.numel())
-        return held * self.k.element_size()
+        return held * self.k.element_size() + (self.cells.bytes() if self.cells else 0)
 
 
 class SequenceCache:
@@ -199,6 +243,8 @@ class SequenceCache:
         self.groups: List[KVGroup] = [
             KVGroup(kv, entries, self.total_pages, self.max_slots, max_seq_len, page_tokens,
                     dtype, device, max_continuation) for kv, entries in by_need.items()]
+        # everything that hands out pages: the groups and their stores of block cells
+        self._stores = list(self.groups) + [g.cells for g in self.groups if g.cells is not None]
         self._where: Dict[int, Tuple[int, int]] = {}
         for gi, g in enumerate(self.groups):
             for li, entry in enumerate(g.entries):
@@ -234,7 +280,7 @@ class SequenceCache:
 
     def release(self, slot: int) -> None:
         self._check_slot(slot)
-        for g in self.groups:
+        for g in self._stores:
             g.pool.give_back(g.pages[slot])
             g.pages[slot] = []
         self._live[slot] = False
@@ -259,24 +305,24 @@ class SequenceCache:
         """Make room for ``n`` more positions in each ``(slot, n)``; either
         every sequence gets its pages or nothing changes."""
         plan = []
-        wanted = [0] * len(self.groups)
+        wanted = [0] * len(self._stores)
         for slot, n in grow:
             self._check_slot(slot)
             new_len = self.lengths[slot] + n
             if n < 0 or new_len > self.max_seq_len:
                 raise ContextOverflow(f"slot {slot}: {self.lengths[slot]} + {n} positions exceed "
                                       f"the maximum sequence length {self.max_seq_len}")
-            for gi, g in enumerate(self.groups):
+            for gi, g in enumerate(self._stores):
                 extra = g.pages_for(new_len) - len(g.pages[slot])
                 if extra > 0:
                     plan.append((gi, slot, extra))
                     wanted[gi] += extra
-        for gi, g in enumerate(self.groups):
+        for gi, g in enumerate(self._stores):
             if wanted[gi] > g.pool.n_free:
                 raise CacheFull(f"the cache holds {self.max_tokens} positions; {wanted[gi]} more "
                                 f"pages of {self.page_tokens} are needed and {g.pool.n_free} are free")
         for gi, slot, extra in plan:
-            g = self.groups[gi]
+            g = self._stores[gi]
             have = len(g.pages[slot])
             new = g.pool.take(extra)
             g.pages[slot].extend(new)
@@ -291,7 +337,7 @@ class SequenceCache:
         """Give back the pages ``slot`` holds beyond what its length needs (what a step
         reserved and then did not use because it failed)."""
         self._check_slot(slot)
-        for g in self.groups:
+        for g in self._stores:
             keep = g.pages_for(self.lengths[slot])
             extra = g.pages[slot][keep:]
             if extra:
@@ -300,7 +346,7 @@ class SequenceCache:
 
     def sync_tables(self) -> None:
         """Bring the device copies of changed page tables up to date."""
-        for g in self.groups:
+        for g in self._stores:
             if g.dirty:
                 g.table.copy_(g.table_host, non_blocking=True)
                 g.dirty = False
@@ -313,7 +359,11 @@ class SequenceCache:
     def kv_view(self, entry: int) -> "KVView":
         gi, li = self._where[entry]
         g = self.groups[gi]
-        return KVView(g.k[li], g.v[li], g.table, g.page_tokens, g.ring_tokens, g.need)
+        c = g.cells
+        if c is None:
+            return KVView(g.k[li], g.v[li], g.table, g.page_tokens, g.ring_tokens, g.need)
+        return KVView(g.k[li], g.v[li], g.table, g.page_tokens, g.ring_tokens, g.need,
+                      c.k[li], c.v[li], c.table, c.page_tokens)
 
     def has_kv(self, entry: int) -> bool:
         return entry in self._where
@@ -325,7 +375,7 @@ class SequenceCache:
         return self.named[name]
 
     def pages_in_use(self) -> int:
-        return sum(g.n_pages - g.pool.n_free for g in self.groups)
+        return sum(g.n_pages - g.pool.n_free for g in self._stores)
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups)
@@ -341,3 +391,9 @@ class KVView:
     page_tokens: int
     ring_tokens: int           # 0: position p lives in cell p
     need: KVNeed
+    # with ``need.pool``: the cells of the blocks, [pages, kv_heads, cell_page_tokens, width],
+    # and their page table [slots, pages of cells per sequence]
+    cell_k: Optional[torch.Tensor] = None
+    cell_v: Optional[torch.Tensor] = None
+    cell_table: Optional[torch.Tensor] = None
+    cell_page_tokens: int = 0

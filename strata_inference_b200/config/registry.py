@@ -22,17 +22,20 @@ class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
+    # (config.json, {tensor name: shape}) -> config.json completed with the sizes that only a
+    # model folder's tensors give; None: config.json says everything
+    sizes_from_tensors: Any = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(names, parse_config, build_spec) -> None:
+def register_architecture(names, parse_config, build_spec, sizes_from_tensors=None) -> None:
     """Add a row.  ``names`` are the strings config.json may carry in
     ``architectures`` or ``model_type``."""
     if isinstance(names, str):
         names = (names,)
-    arch = Architecture(names[0], parse_config, build_spec)
+    arch = Architecture(names[0], parse_config, build_spec, sizes_from_tensors)
     for n in names:
         _ARCHITECTURES[n] = arch
 
@@ -68,9 +71,13 @@ def read_config_json(model_dir: str) -> dict:
             raise ConfigError(f"{path}: not valid JSON ({e})") from None
 
 
-def spec_from_config(config: Mapping[str, Any]) -> Tuple[Any, ModelSpec]:
-    """config.json dictionary -> (typed configuration, model spec)."""
+def spec_from_config(config: Mapping[str, Any],
+                     shapes: Mapping[str, Tuple[int, ...]] = None) -> Tuple[Any, ModelSpec]:
+    """config.json dictionary -> (typed configuration, model spec).  ``shapes``: the shapes of
+    a model folder's tensors by name, for architectures some of whose sizes only they give."""
     arch = architecture_of(config)
+    if shapes is not None and arch.sizes_from_tensors is not None:
+        config = arch.sizes_from_tensors(config, shapes)
     typed = arch.parse_config(config)
     return typed, arch.build_spec(typed)
 
@@ -82,6 +89,8 @@ def _register_builtin() -> None:
     register_architecture(("Karupel", "karupel"), KarupelConfig.from_dict, karupel_spec)
     from .vavupel import VavupelConfig, vavupel_spec
     register_architecture(("Vavupel", "vavupel"), VavupelConfig.from_dict, vavupel_spec)
+    from .gegorax import GegoraxConfig, gegorax_sizes, gegorax_spec
+    register_architecture(("Gegorax", "gegorax"), GegoraxConfig.from_dict, gegorax_spec, gegorax_sizes)
 
 
 _register_builtin()

@@ -57,6 +57,9 @@ class LayerSpec:
     norms: Mapping[str, PartSpec]
     names: Mapping[str, str]
     tensor_names: Mapping[str, Mapping[str, str]] = field(default_factory=dict)
+    # a registered "tail": a part that runs behind the sub-layers on the stream itself
+    # (``names["tail"]`` is what follows the layer's prefix in its tensors' names)
+    tail: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -12,6 +12,10 @@
 // IS its key (the same cell: attention over one shared latent row per position), so the
 // key that was loaded for the score is also what is summed and nothing is read twice; the
 // caller takes the leading columns of the output that it wants.
+// With pooled blocks (`pool` > 0, a window and a second cache of one cell per block of `pool`
+// positions): beside the window's keys the row sees block b's cell if the block's last
+// position is at or before p - window, i.e. the first (p - window + 1) / pool blocks; cells
+// and keys share the one softmax.  The row's keys are then numbered blocks first.
 // Keys at positions >= seq_start[b] (this step's own rows) are read from the
 // step's packed k/v rows when those are given; earlier ones from the cache.
 // With splits > 1 each (row, head) is cut into `splits` runs of keys whose
@@ -44,6 +48,12 @@ struct AttnRowsArgs {
     float scale, softcap;
     const float* sink;      // [n_heads] or null
     int values_in_keys;
+    // blocks of `pool` positions that lie wholly before the window are seen as one key and one
+    // value each (their means), kept in a second paged cache: cell b is block b
+    const void* pk_pool;    // null: no blocks
+    const void* pv_pool;
+    const int* pool_table;
+    int pool, pool_max_pages, pool_page_tokens;
 };
 
 template <typename T> struct Vec16;
@@ -77,6 +87,14 @@ __device__ __forceinline__ const T* key_ptr(const AttnRowsArgs& p, const T* fres
     return pool + (((size_t)page * p.n_kv + g) * p.page_tokens + cell % p.page_tokens) * p.head_dim;
 }
 
+// The cell of block `block` in the cache of pooled blocks.
+template <typename T>
+__device__ __forceinline__ const T* cell_ptr(const AttnRowsArgs& p, const T* pool, int block, int slot,
+                                             int g) {
+    const int page = p.pool_table[(size_t)slot * p.pool_max_pages + block / p.pool_page_tokens];
+    return pool + (((size_t)page * p.n_kv + g) * p.pool_page_tokens + block % p.pool_page_tokens) * p.head_dim;
+}
+
 // One warp per (row, head, split).  Lane l owns the 16-byte vectors number
 // l, l + 32, ... of the head (NI of them at most).
 template <typename T, int NI>
@@ -99,9 +117,10 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
     const int start = p.seq_start[b];
     const int row0 = p.seq_row0[b];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int n = pos - lo + 1;
+    const int nb = p.pk_pool && p.window > 0 && slot >= 0 ? max(0, pos - p.window + 1) / p.pool : 0;
+    const int n = nb + pos - lo + 1;           // keys are numbered lo - nb .. pos: blocks first
     const int chunk = (n + p.splits - 1) / p.splits;
-    const int j0 = lo + split * chunk;
+    const int j0 = lo - nb + split * chunk;
     const int j1 = min(j0 + chunk, pos + 1);
 
     bool live[NI];
@@ -129,7 +148,8 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (j + u < j1) {
-                const T* kp = key_ptr<T>(p, kf, kpool, j + u, start, row0, slot, g);
+                const T* kp = j + u < lo ? cell_ptr<T>(p, (const T*)p.pk_pool, j + u - (lo - nb), slot, g)
+                                         : key_ptr<T>(p, kf, kpool, j + u, start, row0, slot, g);
 #pragma unroll
                 for (int i = 0; i < NI; ++i)
                     if (live[i]) Vec16<T>::load(kp + (lane + 32 * i) * V, kv[u][i]);
@@ -175,7 +195,8 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (j + u < j1 && !p.values_in_keys) {
-                const T* vp = key_ptr<T>(p, vf, vpool, j + u, start, row0, slot, g);
+                const T* vp = j + u < lo ? cell_ptr<T>(p, (const T*)p.pv_pool, j + u - (lo - nb), slot, g)
+                                         : key_ptr<T>(p, vf, vpool, j + u, start, row0, slot, g);
 #pragma unroll
                 for (int i = 0; i < NI; ++i)
                     if (live[i]) Vec16<T>::load(vp + (lane + 32 * i) * V, kv[u][i]);
@@ -333,10 +354,15 @@ SIB_EXPORT int sib_attention_rows(
     int ring_tokens, const int* row_pos, const int* row_seq, const int* seq_slot,
     const int* seq_start, const int* seq_row0, void* out, float* partial, int dtype, int rows,
     int n_heads, int n_kv, int head_dim, float scale, float softcap, int window, int splits,
-    const float* sink, int values_in_keys, void* stream) {
+    const float* sink, int values_in_keys, const void* pk_pool, const void* pv_pool,
+    const int* pool_table, int pool, int pool_max_pages, int pool_page_tokens, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
                 "attention_rows: rows=%d heads=%d kv_heads=%d", rows, n_heads, n_kv);
+    SIB_REQUIRE(pk_pool == nullptr || (pv_pool && pool_table && pool > 0 && pool_max_pages > 0 &&
+                                       pool_page_tokens > 0 && window > 0 && !values_in_keys &&
+                                       ((uintptr_t)pk_pool % 16) == 0 && ((uintptr_t)pv_pool % 16) == 0),
+                "attention_rows: pooled blocks need their cache, a block size and a window");
     SIB_REQUIRE(head_dim >= 16 && head_dim % 16 == 0 && head_dim <= 1024,
                 "attention_rows: head_dim=%d must be a multiple of 16 between 16 and 1024", head_dim);
     SIB_REQUIRE(splits >= 1 && (splits == 1 || partial != nullptr),
@@ -357,7 +383,8 @@ SIB_EXPORT int sib_attention_rows(
     AttnRowsArgs p{q, k_new, v_new, k_pool, v_pool, out, partial, row_pos, row_seq, seq_slot,
                    seq_start, seq_row0, page_table, q_stride, kv_stride, rows, n_heads, n_kv,
                    head_dim, max_pages, page_tokens, ring_tokens, window, splits, scale, softcap,
-                   sink, values_in_keys};
+                   sink, values_in_keys, pk_pool, pv_pool, pool_table, pool, pool_max_pages,
+                   pool_page_tokens};
     const long long units = (long long)rows * n_heads * splits;
     const long long blocks = (units + 3) / 4;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_rows: too many rows (%d)", rows);

@@ -225,8 +225,8 @@ SIB_EXPORT int sib_bigram_embed(const int* tokens, const void* table, const void
 }
 
 // out = act(x), one value per value: the activation of a feed-forward without a gate.
-// act 2: the square of max(x, 0).
-enum { ACT_RELU_SQUARED = 2 };
+// act 2: the square of max(x, 0); act 3: tanh(x).
+enum { ACT_RELU_SQUARED = 2, ACT_TANH = 3 };
 template <typename T>
 __global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, size_t total, int act) {
     pdl_trigger();
@@ -236,6 +236,7 @@ __global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, si
         const float v = to_f32(x[idx]);
         float y;
         if (act == ACT_RELU_SQUARED) { const float p = fmaxf(v, 0.f); y = p * p; }
+        else if (act == ACT_TANH) y = tanhf(v);
         else y = gate_act(v, act);
         out[idx] = from_f32<T>(y);
     }
@@ -243,7 +244,7 @@ __global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, si
 
 SIB_EXPORT int sib_activate(const void* x, void* out, int dtype, long long total, int act, void* stream) {
     if (total == 0) return 0;
-    SIB_REQUIRE(total > 0 && act >= 0 && act <= ACT_RELU_SQUARED, "activate: %lld values, activation %d", total, act);
+    SIB_REQUIRE(total > 0 && act >= 0 && act <= ACT_TANH, "activate: %lld values, activation %d", total, act);
     const long long want = (total + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(activate_kernel<T>, dim3(blocks), dim3(256), 0,
@@ -276,4 +277,38 @@ SIB_EXPORT int sib_pair_rows(const float* a, const float* b, void* out, int out_
     SIB_DISPATCH_DTYPE(out_dtype, sib_launch_chained(pair_rows_kernel<T>, dim3(blocks), dim3(256), 0,
                                                      (cudaStream_t)stream, a, b, (T*)out, hidden, total));
     return sib_check_launch("pair_rows");
+}
+
+// ---------------------------------------------------------------------------
+// gelu_gate_rows: y[r, j] = gelu_tanh(t[r, j]) * e[r, col0 + j]: a gate made from the stream
+// times a slice of a 32-bit row that was gathered for the row's token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const T* __restrict__ t, const float* __restrict__ e,
+                                      long long e_stride, int col0, T* __restrict__ y, int width,
+                                      size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width;
+        const int j = (int)(i - r * width);
+        const float z = to_f32(t[i]);
+        const float g = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        y[i] = from_f32<T>(g * e[r * e_stride + col0 + j]);
+    }
+}
+
+SIB_EXPORT int sib_gelu_gate_rows(const void* t, const float* e, long long e_stride, int col0, void* y,
+                                  int dtype, int rows, int width, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && width > 0 && col0 >= 0 && e_stride >= col0 + width,
+                "gelu_gate_rows: rows=%d width=%d from column %d of %lld", rows, width, col0, e_stride);
+    const size_t total = (size_t)rows * width;
+    const size_t want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(gelu_gate_rows_kernel<T>, dim3(blocks), dim3(256), 0,
+                                                 (cudaStream_t)stream, (const T*)t, e, e_stride, col0,
+                                                 (T*)y, width, total));
+    return sib_check_launch("gelu_gate_rows");
 }

@@ -4,8 +4,8 @@
 //   head_prepare   per row and head, in 32-bit:
 //       x  = proj + bias                                   (bias optional)
 //       q, k: x <- x / sqrt(mean(x^2) + eps) * w           (w optional: no norm without it)
-//       q, k: the first `rot` dimensions rotated in half-split pairs (i, i + rot/2) by
-//             the angle pos * inv_freq[i]; the rest pass
+//       q, k: the first `rot` dimensions rotated in half-split pairs (i, i + rot/2), or in
+//             neighbouring pairs (2i, 2i + 1), by the angle pos * inv_freq[i]; the rest pass
 //       v:    v <- (1 - lambda) v + lambda v_first         (v_first optional)
 //     q, k and v go to a packed buffer whose heads are all `pad` wide (key width and value
 //     width may differ: the narrower one is filled up with zeros, which changes neither a
@@ -37,6 +37,7 @@ struct HeadPrepareArgs {
     int n_heads, n_kv, kd, vd, pad, rot, v_first_pad;
     int max_pages, page_tokens, ring_tokens;
     float eps;
+    int neighbours;            // 1: the rotated pairs are (2i, 2i + 1) instead of (i, i + rot/2)
 };
 
 // One warp per (row, head unit); a block takes 4 units of one row.
@@ -114,7 +115,11 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(HeadPrepareArgs p) {
         float x = 0.f;
         if (d < width) {
             x = mine[d];
-            if (d < 2 * half) {
+            if (d < 2 * half && p.neighbours) {
+                const float ang = (float)pos * p.inv_freq[d >> 1];
+                const float c = cosf(ang), s = sinf(ang);
+                x = (d & 1) ? x * c + mine[d - 1] * s : x * c - mine[d + 1] * s;
+            } else if (d < 2 * half) {
                 const int i = d < half ? d : d - half;
                 const float ang = (float)pos * p.inv_freq[i];
                 const float c = cosf(ang), s = sinf(ang);
@@ -133,7 +138,7 @@ SIB_EXPORT int sib_head_prepare(
     const void* v_first, long long v_first_stride, int v_first_pad, const float* lambda, const int* row_pos,
     const int* row_seq, const int* seq_slot, const int* seq_end, void* k_pool, void* v_pool,
     const int* page_table, int max_pages, int page_tokens, int ring_tokens, int rows, int n_heads,
-    int n_kv, int kd, int vd, int pad, void* stream) {
+    int n_kv, int kd, int vd, int pad, int neighbours, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv >= 0 && kd > 0 && vd > 0,
                 "head_prepare: rows=%d heads=%d kv_heads=%d key width=%d value width=%d", rows,
@@ -151,7 +156,7 @@ SIB_EXPORT int sib_head_prepare(
     HeadPrepareArgs p{proj, qkv, bias, q_gain, k_gain, rot ? inv_freq : nullptr, v_first, lambda,
                       row_pos, row_seq, seq_slot, seq_end, k_pool, v_pool, page_table, proj_stride,
                       v_first_stride, n_heads, n_kv, kd, vd, pad, rot, v_first_pad, max_pages, page_tokens,
-                      ring_tokens, eps};
+                      ring_tokens, eps, neighbours};
     const int units = n_heads + 2 * n_kv;
     const size_t smem = (size_t)4 * pad * sizeof(float);
     SIB_REQUIRE(smem <= 48 * 1024, "head_prepare: heads of %d are too wide", pad);
@@ -159,6 +164,85 @@ SIB_EXPORT int sib_head_prepare(
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(head_prepare_kernel<T>, dim3(rows, (units + 3) / 4),
                                                  dim3(128), smem, (cudaStream_t)stream, p));
     return sib_check_launch("head_prepare");
+}
+
+// ---------------------------------------------------------------------------
+// pool_store: one more cell per block of `pool` positions for an attention that sees far
+// tokens only as blocks: the mean of the block's keys and the mean of its values, as the
+// packed rows and the cache hold them, written into a second paged cache whose cell b stands
+// for the positions b pool .. b pool + pool - 1.  A block is written by the step that brings
+// its last position; positions of the block that earlier steps brought are read from the
+// (ring) cache, the step's own from its packed rows.
+// grid (blocks a sequence can complete in this step, kv heads, sequences); thread d of pad.
+// ---------------------------------------------------------------------------
+struct PoolStoreArgs {
+    const void* qkv;           // [rows, (n_heads + 2 n_kv) * pad]
+    const void* k_pool;        // [pages, n_kv, page_tokens, pad]: earlier positions
+    const void* v_pool;
+    const int* page_table;
+    void* pk_pool;             // [pages, n_kv, pool_page_tokens, pad]: the blocks' cells
+    void* pv_pool;
+    const int* pool_table;
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_end;
+    const int* seq_row0;
+    int n_heads, n_kv, pad, pool;
+    int max_pages, page_tokens, ring_tokens, pool_max_pages, pool_page_tokens;
+};
+
+template <typename T>
+__global__ void pool_store_kernel(PoolStoreArgs p) {
+    pdl_trigger();
+    const int b = blockIdx.z, g = blockIdx.y;
+    const int slot = p.seq_slot[b];
+    const int start = p.seq_start[b], end = p.seq_end[b], row0 = p.seq_row0[b];
+    const int block = start / p.pool + blockIdx.x;
+    if (slot < 0 || block >= end / p.pool) return;
+    pdl_wait();
+    const int units = p.n_heads + 2 * p.n_kv;
+    const int page = p.pool_table[(size_t)slot * p.pool_max_pages + block / p.pool_page_tokens];
+    const size_t cell = (((size_t)page * p.n_kv + g) * p.pool_page_tokens + block % p.pool_page_tokens) * p.pad;
+    for (int d = threadIdx.x; d < 2 * p.pad; d += blockDim.x) {
+        const bool is_v = d >= p.pad;
+        const int e = is_v ? d - p.pad : d;
+        float sum = 0.f;
+        for (int j = block * p.pool; j < (block + 1) * p.pool; ++j) {
+            if (j >= start) {
+                const int unit = p.n_heads + (is_v ? p.n_kv : 0) + g;
+                sum += to_f32(((const T*)p.qkv)[((size_t)(row0 + j - start) * units + unit) * p.pad + e]);
+            } else {
+                const int at = p.ring_tokens > 0 ? j % p.ring_tokens : j;
+                const int pg = p.page_table[(size_t)slot * p.max_pages + at / p.page_tokens];
+                const T* src = (const T*)(is_v ? p.v_pool : p.k_pool);
+                sum += to_f32(src[(((size_t)pg * p.n_kv + g) * p.page_tokens + at % p.page_tokens) * p.pad + e]);
+            }
+        }
+        ((T*)(is_v ? p.pv_pool : p.pk_pool))[cell + e] = from_f32<T>(sum / (float)p.pool);
+    }
+}
+
+SIB_EXPORT int sib_pool_store(const void* qkv, const void* k_pool, const void* v_pool,
+                              const int* page_table, int max_pages, int page_tokens, int ring_tokens,
+                              void* pk_pool, void* pv_pool, const int* pool_table, int pool_max_pages,
+                              int pool_page_tokens, const int* seq_slot, const int* seq_start,
+                              const int* seq_end, const int* seq_row0, int dtype, int n_seqs,
+                              int max_count, int n_heads, int n_kv, int pad, int pool, void* stream) {
+    if (n_seqs == 0 || max_count == 0) return 0;
+    SIB_REQUIRE(n_seqs > 0 && n_seqs < 65536 && n_kv > 0 && n_kv < 65536 && pad > 0 && pool > 0 && max_count > 0,
+                "pool_store: sequences=%d kv_heads=%d width=%d pool=%d", n_seqs, n_kv, pad, pool);
+    SIB_REQUIRE(qkv && k_pool && v_pool && page_table && pk_pool && pv_pool && pool_table &&
+                    page_tokens > 0 && max_pages > 0 && pool_page_tokens > 0 && pool_max_pages > 0,
+                "pool_store: incomplete cache description");
+    PoolStoreArgs p{qkv, k_pool, v_pool, page_table, pk_pool, pv_pool, pool_table, seq_slot, seq_start,
+                    seq_end, seq_row0, n_heads, n_kv, pad, pool, max_pages, page_tokens, ring_tokens,
+                    pool_max_pages, pool_page_tokens};
+    // a step of c positions completes at most (c + pool - 1) / pool blocks of a sequence
+    const dim3 grid((max_count + pool - 1) / pool, n_kv, n_seqs);
+    const int threads = 2 * pad < 256 ? (2 * pad + 31) / 32 * 32 : 256;
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(pool_store_kernel<T>, grid, dim3(threads), 0,
+                                                 (cudaStream_t)stream, p));
+    return sib_check_launch("pool_store");
 }
 
 // y[r, h * vd + e] = o[r, h * pad + e] * sigmoid(gate[r * gate_stride + h])

@@ -496,3 +496,41 @@ SIB_EXPORT int sib_add_dyt_norm(const void* a, int dtype, const float* post_w, c
                                                  hidden, total));
     return sib_check_launch("add_dyt_norm");
 }
+
+// ---------------------------------------------------------------------------
+// pair_norm_mean: the joint output of two mixers that ran side by side on the same input:
+//     y = (a / rms(a) * wa + b / rms(b) * wb) / 2          (rms over the row, eps inside the root)
+// One block per row; statistics and sum in 32-bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+pair_norm_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
+                      const float* __restrict__ wb, T* __restrict__ y, int width, float eps) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    const T* ar = a + r * width;
+    const T* br = b + r * width;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float x = to_f32(ar[c]), z = to_f32(br[c]);
+        sa += x * x;
+        sb += z * z;
+    }
+    const float ia = 1.0f / sqrtf(block_sum(sa, scratch) / (float)width + eps);
+    const float ib = 1.0f / sqrtf(block_sum(sb, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        y[r * width + c] = from_f32<T>(0.5f * (to_f32(ar[c]) * ia * wa[c] + to_f32(br[c]) * ib * wb[c]));
+}
+
+SIB_EXPORT int sib_pair_norm_mean(const void* a, const void* b, const float* wa, const float* wb,
+                                  void* y, int dtype, int rows, int width, float eps, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && width > 0 && a && b && wa && wb && y, "pair_norm_mean: rows=%d width=%d",
+                rows, width);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(pair_norm_mean_kernel<T>, dim3(rows), dim3(256), 0,
+                                                 (cudaStream_t)stream, (const T*)a, (const T*)b, wa,
+                                                 wb, (T*)y, width, eps));
+    return sib_check_launch("pair_norm_mean");
+}

@@ -15,6 +15,8 @@
 //            with one more column whose v is 1: it holds n, and its output is <n, q>.
 //   retention:  S <- d S + k v^T,  o = S^T q  with one fixed decay d per head:
 //            S_j <- d S_j + v_j k,  o_j = d <S_j, q> + v_j <k, q>
+//   gated:   S <- a S + b k v^T,  o = S^T q  with a and b given per row and head (the
+//            state-space layer: k = B, q = C, v = x, a = exp(-exp(A_log) dt), b = dt)
 //
 // State of a slot: [heads][columns][kd] floats (a column's rows together), then for the
 // memory [heads] running maxima.  The delta rule's convolution history lies behind its
@@ -162,7 +164,9 @@ __global__ void conv_history_kernel(const T* __restrict__ proj, long long stride
 // ---------------------------------------------------------------------------
 // The recurrences.
 // ---------------------------------------------------------------------------
-enum { SCAN_DELTA = 0, SCAN_MEMORY = 1, SCAN_RETENTION = 2 };
+// SCAN_GATED: S <- keep S + take k v^T with keep and take given per row and head (a state-space
+// layer's discretised decay and step size): the memory's update with ready-made factors.
+enum { SCAN_DELTA = 0, SCAN_MEMORY = 1, SCAN_RETENTION = 2, SCAN_GATED = 3 };
 
 struct ScanArgs {
     const void* q;           // row r, key head g at q + r * q_stride + g * kd
@@ -299,7 +303,7 @@ __global__ void __launch_bounds__(kScanThreads) recurrent_scan_kernel(ScanArgs p
             rg = from_f32<TG>(0.f);
             if (t0 + t < n) {
                 const size_t r = (size_t)(row0 + t0 + t);
-                if (MODE == SCAN_DELTA)
+                if (MODE == SCAN_DELTA || MODE == SCAN_GATED)
                     rg = ((const TG*)(tid < kChunk ? p.decay : p.beta))[r * p.H + h];
                 else
                     rg = ((const TG*)(tid < kChunk ? p.gate_i : p.gate_f))[r * p.gate_stride + h];
@@ -629,6 +633,158 @@ SIB_EXPORT int sib_retention_scan(const float* qn, const float* kn, const float*
                seq_slot, seq_start, seq_end, seq_row0, (long long)H * kd, (long long)H * kd,
                (long long)H * vd, 0, state_stride, H, H, kd, vd, 1.0f, 0.f, head_decay};
     return launch_scan<SCAN_RETENTION, float, float>(p, n_seqs, (cudaStream_t)stream);
+}
+
+// The gated recurrence over 32-bit rows: q, k (key heads of kd, G of them) and v (H heads of vd)
+// are given with their row strides (they may be columns of one buffer); keep, take: [rows, H].
+SIB_EXPORT int sib_gated_scan(const float* q, const float* k, const float* v, long long q_stride,
+                              long long k_stride, long long v_stride, const float* keep,
+                              const float* take, float* state, long long state_stride, float* out,
+                              const int* seq_slot, const int* seq_start, const int* seq_end,
+                              const int* seq_row0, int rows, int n_seqs, int H, int G, int kd, int vd,
+                              void* stream) {
+    if (rows == 0) return 0;
+    if (check_scan("gated_scan", rows, n_seqs, H, G, kd, vd)) return -1;
+    SIB_REQUIRE(keep != nullptr && take != nullptr, "gated_scan: the rows' factors are needed");
+    ScanArgs p{q, k, v, keep, take, nullptr, nullptr, nullptr, nullptr, state, out, nullptr,
+               seq_slot, seq_start, seq_end, seq_row0, q_stride, k_stride, v_stride, 0, state_stride,
+               H, G, kd, vd, 1.0f, 0.f};
+    return launch_scan<SCAN_GATED, float, float>(p, n_seqs, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------
+// The state-space layer around its recurrence.
+//   ssm_prepare   per row: the causal convolution (with bias) and silu of the channels
+//       x (H vd) | B (G N) | C (G N) of a projected row z | x | B | C | dt, the step size
+//       dt = softplus(dt + dt_bias) and the decay exp(-exp(A_log) dt) per head, all 32-bit;
+//       inputs before the step come from the slot's history [taps - 1][channels].
+//   ssm_finish    y = (o + D_h x) * silu(z), divided by its root mean square in `parts`
+//       equal parts of a row, times a weight.
+// ---------------------------------------------------------------------------
+struct SsmPrepareArgs {
+    const void* proj;        // [rows, stride]: z (inner) | x (inner) | B | C | dt (H)
+    const float* conv_w;     // [channels, taps], last tap the row's own
+    const float* conv_b;     // [channels]
+    const float* a_log;      // [H]
+    const float* dt_bias;    // [H]
+    const float* state;      // [slots, state_stride]; the history starts at hist_offset
+    float* xbc;              // [rows, channels]
+    float* keep;             // [rows, H]
+    float* take;             // [rows, H]
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_row0;
+    long long stride, state_stride, hist_offset;
+    int H, inner, channels, taps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) ssm_prepare_kernel(SsmPrepareArgs p) {
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= p.channels + p.H) return;
+    const int pos = p.row_pos[r];
+    const int b = p.row_seq[r];
+    const int slot = p.seq_slot[b];
+    const int start = p.seq_start[b], row0 = p.seq_row0[b];
+    pdl_wait();
+    const T* proj = (const T*)p.proj;
+    if (c >= p.channels) {
+        const int h = c - p.channels;
+        const float dt = softplus_f(to_f32(proj[(size_t)r * p.stride + p.inner + p.channels + h]) + p.dt_bias[h]);
+        p.keep[(size_t)r * p.H + h] = expf(-expf(p.a_log[h]) * dt);
+        p.take[(size_t)r * p.H + h] = dt;
+        return;
+    }
+    const float* hist = slot >= 0 ? p.state + (size_t)slot * p.state_stride + p.hist_offset : nullptr;
+    float y = p.conv_b[c];
+    for (int j = 0; j < p.taps; ++j) {
+        const int at = pos - (p.taps - 1) + j;
+        float x = 0.f;
+        if (at >= start) x = to_f32(proj[(size_t)(row0 + at - start) * p.stride + p.inner + c]);
+        else if (hist) x = hist[(size_t)(at - start + p.taps - 1) * p.channels + c];
+        y += p.conv_w[(size_t)c * p.taps + j] * x;
+    }
+    p.xbc[(size_t)r * p.channels + c] = silu_f(y);
+}
+
+SIB_EXPORT int sib_ssm_prepare(const void* proj, long long stride, int dtype, const float* conv_w,
+                               const float* conv_b, const float* a_log, const float* dt_bias,
+                               float* state, long long state_stride, long long hist_offset,
+                               float* xbc, float* keep, float* take, const int* row_pos,
+                               const int* row_seq, const int* seq_slot, const int* seq_start,
+                               const int* seq_end, const int* seq_row0, int rows, int n_seqs, int H,
+                               int inner, int channels, int taps, void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && n_seqs > 0 && n_seqs < 65536 && H > 0 && inner > 0 && channels >= inner,
+                "ssm_prepare: rows=%d sequences=%d heads=%d inner=%d channels=%d", rows, n_seqs, H,
+                inner, channels);
+    SIB_REQUIRE(taps >= 1 && taps <= 64, "ssm_prepare: %d taps", taps);
+    SsmPrepareArgs p{proj, conv_w, conv_b, a_log, dt_bias, state, xbc, keep, take, row_pos, row_seq,
+                     seq_slot, seq_start, seq_row0, stride, state_stride, hist_offset, H, inner,
+                     channels, taps};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int by = (channels + H + 255) / 256;
+    SIB_REQUIRE(by < 65536, "ssm_prepare: too many channels (%d)", channels);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(ssm_prepare_kernel<T>, dim3(rows, by), dim3(256), 0, s, p));
+    int rc = sib_check_launch("ssm_prepare");
+    if (rc || taps == 1) return rc;
+    // the history after the step: the channels begin `inner` columns into a projected row
+    const size_t esz = dtype == SIB_F32 ? 4 : 2;
+    const char* first = (const char*)proj + (size_t)inner * esz;
+    const dim3 grid((channels + 255) / 256, n_seqs);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(conv_history_kernel<T>, grid, dim3(256), 0, s,
+                                                 (const T*)first, stride, state, state_stride,
+                                                 hist_offset, seq_slot, seq_start, seq_end, seq_row0,
+                                                 channels, taps));
+    return sib_check_launch("conv_history");
+}
+
+// One warp per (row, part of the row).
+template <typename T>
+__global__ void __launch_bounds__(128)
+ssm_finish_kernel(const float* __restrict__ o, const float* __restrict__ xbc, long long x_stride,
+                  const T* __restrict__ z, long long z_stride, const float* __restrict__ skip,
+                  const float* __restrict__ w, T* __restrict__ y, int rows, int inner, int vd,
+                  int parts, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (unit >= (long long)rows * parts) return;
+    const size_t r = unit / parts;
+    const int part = (int)(unit % parts), len = inner / parts, e0 = part * len;
+    auto value = [&](int e) {
+        const float zz = to_f32(z[r * z_stride + e]);
+        return (o[r * inner + e] + skip[e / vd] * xbc[r * x_stride + e]) * silu_f(zz);
+    };
+    float ss = 0.f;
+    for (int e = e0 + lane; e < e0 + len; e += 32) {
+        const float v = value(e);
+        ss += v * v;
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)len + eps);
+    for (int e = e0 + lane; e < e0 + len; e += 32)
+        y[r * inner + e] = from_f32<T>(value(e) * inv * w[e]);
+}
+
+SIB_EXPORT int sib_ssm_finish(const float* o, const float* xbc, long long x_stride, const void* z,
+                              long long z_stride, const float* skip, const float* w, void* y,
+                              int dtype, int rows, int inner, int vd, int parts, float eps,
+                              void* stream) {
+    if (rows == 0) return 0;
+    SIB_REQUIRE(rows > 0 && inner > 0 && vd > 0 && inner % vd == 0 && parts > 0 && inner % parts == 0,
+                "ssm_finish: rows=%d inner=%d head width=%d parts=%d", rows, inner, vd, parts);
+    const long long blocks = ((long long)rows * parts + 3) / 4;
+    SIB_REQUIRE(blocks < (1ll << 31), "ssm_finish: too many rows (%d)", rows);
+    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(ssm_finish_kernel<T>, dim3((unsigned)blocks), dim3(128),
+                                                 0, (cudaStream_t)stream, o, xbc, x_stride,
+                                                 (const T*)z, z_stride, skip, w, (T*)y, rows, inner,
+                                                 vd, parts, eps));
+    return sib_check_launch("ssm_finish");
 }
 
 // ---------------------------------------------------------------------------

@@ -93,9 +93,10 @@ class Engine:
         chosen by the architecture named in config.json."""
         from ..weights.safetensors_io import ModelFiles
         config = read_config_json(model_dir)
-        _, spec = spec_from_config(config)
+        files = ModelFiles(model_dir)
+        _, spec = spec_from_config(config, {n: tuple(files.shape(n)) for n in files.names()})
         native.require_device(torch.device(kw.get("device", "cuda:0")))
-        return cls(spec, FileSource(ModelFiles(model_dir)), dtype, where=model_dir, **kw)
+        return cls(spec, FileSource(files), dtype, where=model_dir, **kw)
 
     @classmethod
     def from_random(cls, config: Mapping, seed: int, dtype="bfloat16", matrix_std: float = None,

@@ -50,6 +50,9 @@ def _sites(spec: ModelSpec):
         for site, norm in layer.norms.items():
             yield (layer.prefix + layer.names[site], parts.part_class("norm", norm.kind),
                    (norm.params, H), layer.tensor_names.get(site, {}))
+        if layer.tail is not None:
+            yield (layer.prefix + layer.names["tail"], parts.part_class("tail", layer.tail.kind),
+                   (layer.tail.params, H), layer.tensor_names.get("tail", {}))
     if spec.pass_mix is not None:
         yield (spec.names["pass_mix"], parts.part_class("joint", spec.pass_mix.kind),
                (spec.pass_mix.params, H), spec.tensor_names.get("pass_mix", {}))
@@ -118,7 +121,11 @@ class DecoderModel:
             norms = {site: parts.part_class("norm", n.kind)(
                 n.params, H, _sub(weights, layer.prefix + layer.names[site]), rt)
                 for site, n in layer.norms.items()}
-            self.blocks.append(parts.part_class("block", layer.block)(mixer, ff, norms, rt))
+            extra = {}
+            if layer.tail is not None:
+                extra["tail"] = parts.part_class("tail", layer.tail.kind)(
+                    layer.tail.params, H, _sub(weights, layer.prefix + layer.names["tail"]), rt)
+            self.blocks.append(parts.part_class("block", layer.block)(mixer, ff, norms, rt, **extra))
         self.pass_mix = None
         if spec.pass_mix is not None:
             self.pass_mix = parts.part_class("joint", spec.pass_mix.kind)(

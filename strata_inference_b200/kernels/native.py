@@ -25,6 +25,7 @@ GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
 ACT_RELU_SQUARED = 2                    # of the feed-forward without a gate (activate)
+ACT_TANH = 3                            # tanh, value by value (activate)
 GATE_SILU, GATE_SIGMOID = 0, 1          # of head_norm_gate
 
 _lib = None
@@ -449,7 +450,7 @@ def bigram_embed(ctx, table: torch.Tensor, bigram: torch.Tensor, last_token: tor
 
 @_timed(lambda x, out, act: ("activate", _nbytes(x, out), 0))
 def activate(x: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
-    """out = act(x) value by value (ACT_RELU_SQUARED: max(x, 0) squared)."""
+    """out = act(x) value by value (ACT_RELU_SQUARED: max(x, 0) squared; ACT_TANH)."""
     _want(x, out.dtype, "x")
     _want(out, out.dtype, "out")
     if x.numel() != out.numel():
@@ -470,6 +471,124 @@ def pair_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tens
         raise KernelError("pair_rows: shapes do not fit")
     _check(library().sib_pair_rows(_ptr(a), _ptr(b), _ptr(out), _code(out.dtype), c_int(rows),
                                    c_int(hidden), _stream()))
+    return out
+
+
+@_timed(lambda t, e, col0, y: ("gelu_gate_rows", _nbytes(t, y) * 2, 0))
+def gelu_gate_rows(t: torch.Tensor, e: torch.Tensor, col0: int, y: torch.Tensor) -> torch.Tensor:
+    """y[r, j] = gelu_tanh(t[r, j]) * e[r, col0 + j]; ``e`` 32-bit rows (a view is fine)."""
+    _want(t, y.dtype, "t")
+    _want(y, y.dtype, "y")
+    _want(e, torch.float32, "e", contiguous=False)
+    rows, width = t.shape
+    if tuple(y.shape) != (rows, width) or e.shape[0] != rows or e.stride(1) != 1 or e.shape[1] < col0 + width:
+        raise KernelError("gelu_gate_rows: shapes do not fit")
+    _check(library().sib_gelu_gate_rows(_ptr(t), _ptr(e), c_longlong(e.stride(0)), c_int(col0), _ptr(y),
+                                        _code(y.dtype), c_int(rows), c_int(width), _stream()))
+    return y
+
+
+@_timed(lambda a, b, wa, wb, y, eps: ("pair_norm_mean", _nbytes(a, b, y), 0))
+def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
+                   y: torch.Tensor, eps: float) -> torch.Tensor:
+    """y = (a / rms(a) * wa + b / rms(b) * wb) / 2 row by row (csrc/norm.cu); statistics and
+    the sum are 32-bit."""
+    rows, width = y.shape
+    for t, nm in ((a, "a"), (b, "b"), (y, "y")):
+        _want(t, y.dtype, nm)
+        if tuple(t.shape) != (rows, width):
+            raise KernelError("pair_norm_mean: shapes do not fit")
+    _f32(wa, width, "wa")
+    _f32(wb, width, "wb")
+    _check(library().sib_pair_norm_mean(_ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(y), _code(y.dtype),
+                                        c_int(rows), c_int(width), c_float(eps), _stream()))
+    return y
+
+
+@_timed(lambda logits, bias, ids, weights: ("router_topk", _nbytes(logits, ids, weights), 0))
+def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
+                weights: torch.Tensor) -> None:
+    """Per row of the 32-bit ``logits`` (+ ``bias``): the ``top`` = ids.shape[1] largest (ties: the
+    lower index) into ``ids`` (int32) and the softmax over those alone into ``weights``."""
+    rows, experts = logits.shape
+    top = ids.shape[1]
+    _want(logits, torch.float32, "logits")
+    _want(ids, torch.int32, "ids")
+    _f32(weights, rows * top, "weights")
+    if bias is not None:
+        _f32(bias, experts, "bias")
+    if ids.shape[0] != rows:
+        raise KernelError("router_topk: one row of choices per row of logits")
+    _check(library().sib_router_topk(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), c_int(rows),
+                                     c_int(experts), c_int(top), _stream()))
+
+
+@_timed(lambda gu, y, row_weight, limit, alpha: ("expert_activate", _nbytes(gu, y), 0))
+def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torch.Tensor],
+                    limit: float, alpha: float) -> torch.Tensor:
+    """y = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit),
+    from rows ``[gate (ff) | up (ff)]``; with ``row_weight`` every row times its 32-bit weight."""
+    rows, ff = y.shape
+    _want(gu, y.dtype, "gu", contiguous=False)
+    _want(y, y.dtype, "y")
+    if gu.shape[0] != rows or gu.shape[1] != 2 * ff or gu.stride(1) != 1:
+        raise KernelError("expert_activate: rows of gate | up")
+    if row_weight is not None:
+        _f32(row_weight, rows, "row_weight")
+    _check(library().sib_expert_activate(_ptr(gu), c_longlong(gu.stride(0)), _ptr(y), _ptr(row_weight),
+                                         _code(y.dtype), c_int(rows), c_int(ff), c_float(limit),
+                                         c_float(alpha), _stream()))
+    return y
+
+
+@_timed(lambda x, w_gu, w_down, ids, weights, base, out, limit, alpha: (
+    "routed_rows", ids.numel() * 3 * w_down.shape[1] * w_down.shape[2] * x.element_size(),
+    6.0 * ids.numel() * w_down.shape[1] * w_down.shape[2]))
+def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                weights: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor,
+                limit: float, alpha: float) -> torch.Tensor:
+    """The chosen experts of every row, each (row, expert) pair streaming its expert's matrices
+    (csrc/routed.cu): ``w_gu`` ``[experts, 2 ff, width]`` (gate rows, then up rows), ``w_down``
+    ``[experts, width, ff]``; out = base + sum_k weights[r, k] down(act(gate, up)) in 32-bit."""
+    rows, width = x.shape
+    top = ids.shape[1]
+    experts, _, ff = w_down.shape
+    _want(x, x.dtype, "x", contiguous=False)
+    for t, nm in ((w_gu, "w_gu"), (w_down, "w_down"), (out, "out")):
+        _want(t, x.dtype, nm)
+    _want(ids, torch.int32, "ids")
+    _f32(weights, rows * top, "weights")
+    if tuple(w_gu.shape) != (experts, 2 * ff, width) or w_down.shape[1] != width or x.stride(1) != 1 \
+            or tuple(out.shape) != (rows, width) or ids.shape[0] != rows:
+        raise KernelError("routed_rows: shapes do not fit")
+    if base is not None:
+        _want(base, x.dtype, "base")
+    mid = torch.empty((rows * top, ff), dtype=x.dtype, device=x.device)
+    _check(library().sib_routed_rows(
+        _ptr(x), c_longlong(x.stride(0)), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
+        _ptr(base), _ptr(mid), _ptr(out), _code(x.dtype), c_int(rows), c_int(width), c_int(ff),
+        c_int(top), c_float(limit), c_float(alpha), _stream()))
+    return out
+
+
+@_timed(lambda ys, where, weights, base, out: ("routed_combine", _nbytes(ys, out), 0))
+def routed_combine(ys: torch.Tensor, where: torch.Tensor, weights: torch.Tensor,
+                   base: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """out[r] = base[r] + sum_k weights[r, k] ys[where[r, k]] in 32-bit: the rows' sums over the
+    outputs of their (row, expert) pairs, which lie sorted by expert."""
+    rows, width = out.shape
+    top = where.shape[1]
+    _want(ys, out.dtype, "ys")
+    _want(out, out.dtype, "out")
+    _want(where, torch.int32, "where")
+    _f32(weights, rows * top, "weights")
+    if ys.shape[1] != width or where.shape[0] != rows:
+        raise KernelError("routed_combine: shapes do not fit")
+    if base is not None:
+        _want(base, out.dtype, "base")
+    _check(library().sib_routed_combine(_ptr(ys), _ptr(where), _ptr(weights), _ptr(base), _ptr(out),
+                                        _code(out.dtype), c_int(rows), c_int(width), c_int(top),
+                                        _stream()))
     return out
 
 
@@ -510,10 +629,12 @@ def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Ten
                  v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor], row_pos, row_seq,
                  seq_slot, seq_end, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
                  page_table: Optional[torch.Tensor], page_tokens: int, ring_tokens: int,
-                 n_heads: int, n_kv: int, key_dim: int, value_dim: int, pad: int) -> torch.Tensor:
+                 n_heads: int, n_kv: int, key_dim: int, value_dim: int, pad: int,
+                 style: int = ROPE_HALF_SPLIT) -> torch.Tensor:
     """From a projected row ``[q heads | k heads | v heads | ...]`` to the packed q|k|v rows
     the attention kernels read, heads ``pad`` wide (csrc/head_prepare.cu): bias, per-head RMS
-    norm of q and k with a gain, partial rotation, values mixed with ``v_first`` (a view
+    norm of q and k with a gain, partial rotation (``style``: half-split pairs or
+    neighbouring ones), values mixed with ``v_first`` (a view
     ``[rows, n_kv * its own head width]`` of an earlier layer's packed rows) by ``lam``, and
     k and v written into the paged cache."""
     rows = proj.shape[0]
@@ -553,8 +674,33 @@ def head_prepare(proj: torch.Tensor, qkv: torch.Tensor, bias: Optional[torch.Ten
         _ptr(v_first), c_longlong(v_stride), c_int(v_pad), _ptr(lam), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot),
         _ptr(seq_end), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), c_int(max_pages),
         c_int(page_tokens), c_int(ring_tokens), c_int(rows), c_int(n_heads), c_int(n_kv),
-        c_int(key_dim), c_int(value_dim), c_int(pad), _stream()))
+        c_int(key_dim), c_int(value_dim), c_int(pad), c_int(1 if style == ROPE_INTERLEAVED else 0),
+        _stream()))
     return qkv
+
+
+@_timed(lambda qkv, view, *a, **kw: ("pool_store", 2 * _nbytes(qkv) // 3, 0))
+def pool_store(qkv: torch.Tensor, view, ctx, n_heads: int, n_kv: int, pad: int) -> None:
+    """For every block of ``view.need.pool`` positions whose last position this step brings:
+    the mean of the block's keys and the mean of its values, as the packed rows ``qkv`` (this
+    step's positions) and the cache ``view`` (earlier ones) hold them, into the block's cells
+    (csrc/head_prepare.cu pool_store)."""
+    _want(qkv, qkv.dtype, "qkv")
+    if view.cell_k is None or view.need.pool <= 0:
+        raise KernelError("pool_store: the cache keeps no cells of blocks")
+    if tuple(qkv.shape) != (ctx.n_rows, (n_heads + 2 * n_kv) * pad):
+        raise KernelError("pool_store: the packed rows do not fit the head counts")
+    for t in (view.k, view.v, view.cell_k, view.cell_v):
+        _want(t, qkv.dtype, "cache")
+        if t.shape[1] != n_kv or t.shape[3] != pad:
+            raise KernelError("pool_store: keys and values must be cached `pad` wide")
+    _check(library().sib_pool_store(
+        _ptr(qkv), _ptr(view.k), _ptr(view.v), _ptr(view.page_table), c_int(view.page_table.shape[1]),
+        c_int(view.page_tokens), c_int(view.ring_tokens), _ptr(view.cell_k), _ptr(view.cell_v),
+        _ptr(view.cell_table), c_int(view.cell_table.shape[1]), c_int(view.cell_page_tokens),
+        _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0),
+        _code(qkv.dtype), c_int(ctx.n_seqs), c_int(ctx.max_count), c_int(n_heads), c_int(n_kv),
+        c_int(pad), c_int(view.need.pool), _stream()))
 
 
 @_timed(lambda o, gate, y, *a: ("head_gate", _nbytes(o, y), 0))
@@ -826,6 +972,133 @@ def head_norm_gate(o: torch.Tensor, m: Optional[torch.Tensor], w: Optional[torch
     return y
 
 
+@_timed(lambda q, k, v, keep, take, state, out, ctx, n_heads, n_kv, key_dim, value_dim: _scan_work(
+    "gated_scan", out.shape[0], ctx.n_seqs, n_heads, key_dim, value_dim))
+def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, keep: torch.Tensor,
+               take: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int,
+               n_kv: int, key_dim: int, value_dim: int) -> torch.Tensor:
+    """S <- keep S + take k v^T, o = S^T q with ``keep`` and ``take`` 32-bit ``[rows, heads]``
+    (csrc/recurrent.cu).  ``q``, ``k`` (``n_kv`` key heads of ``key_dim``) and ``v`` (``n_heads``
+    heads of ``value_dim``) are 32-bit views whose rows may be columns of one buffer."""
+    rows = out.shape[0]
+    _want(state, torch.float32, "state")
+    for t, n, nm in ((q, n_kv * key_dim, "q"), (k, n_kv * key_dim, "k"), (v, n_heads * value_dim, "v")):
+        _want(t, torch.float32, nm, contiguous=False)
+        if tuple(t.shape) != (rows, n) or t.stride(1) != 1:
+            raise KernelError(f"gated_scan: {nm} must be [rows, {n}] with unit column stride")
+    _f32(keep, rows * n_heads, "keep")
+    _f32(take, rows * n_heads, "take")
+    _f32(out, rows * n_heads * value_dim, "out")
+    if state.shape[1] < n_heads * value_dim * key_dim:
+        raise KernelError("gated_scan: the state is too small for the matrices")
+    _check(library().sib_gated_scan(
+        _ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
+        c_longlong(v.stride(0)), _ptr(keep), _ptr(take), _ptr(state), c_longlong(state.stride(0)),
+        _ptr(out), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0),
+        c_int(rows), c_int(ctx.n_seqs), c_int(n_heads), c_int(n_kv), c_int(key_dim),
+        c_int(value_dim), _stream()))
+    return out
+
+
+@_timed(lambda proj, conv_w, conv_b, a_log, dt_bias, state, hist_offset, xbc, keep, take, *a, **kw: (
+    "ssm_prepare", _nbytes(proj, xbc, keep, take), 0))
+def ssm_prepare(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, a_log: torch.Tensor,
+                dt_bias: torch.Tensor, state: torch.Tensor, hist_offset: int, xbc: torch.Tensor,
+                keep: torch.Tensor, take: torch.Tensor, ctx, n_heads: int, inner: int,
+                channels: int, taps: int) -> None:
+    """First step of the state-space layer (csrc/recurrent.cu): from projected rows
+    ``[z (inner) | x (inner) | B | C | dt (heads)]`` the convolved (with bias) and activated
+    channels x | B | C, the step size softplus(dt + dt_bias) (``take``) and the decay
+    exp(-exp(A_log) step) (``keep``), all 32-bit; then every sequence's convolution history
+    (``state[slot, hist_offset:]``, ``[taps - 1, channels]``) is brought up to the step's end."""
+    rows = proj.shape[0]
+    _want(proj, proj.dtype, "proj")
+    _want(state, torch.float32, "state")
+    if proj.shape[1] != inner + channels + n_heads:
+        raise KernelError("ssm_prepare: a projected row must hold z, the channels and dt")
+    _f32(conv_w, channels * taps, "conv_w")
+    _f32(conv_b, channels, "conv_b")
+    _f32(a_log, n_heads, "a_log")
+    _f32(dt_bias, n_heads, "dt_bias")
+    _f32(xbc, rows * channels, "xbc")
+    _f32(keep, rows * n_heads, "keep")
+    _f32(take, rows * n_heads, "take")
+    if state.shape[1] < hist_offset + (taps - 1) * channels:
+        raise KernelError("ssm_prepare: the state is too small for the history")
+    _check(library().sib_ssm_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), _code(proj.dtype), _ptr(conv_w), _ptr(conv_b),
+        _ptr(a_log), _ptr(dt_bias), _ptr(state), c_longlong(state.stride(0)), c_longlong(hist_offset),
+        _ptr(xbc), _ptr(keep), _ptr(take), _ptr(ctx.row_pos), _ptr(ctx.row_seq), _ptr(ctx.seq_slot),
+        _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0), c_int(rows), c_int(ctx.n_seqs),
+        c_int(n_heads), c_int(inner), c_int(channels), c_int(taps), _stream()))
+
+
+@_timed(lambda o, xbc, z, skip, w, y, *a: ("ssm_finish", 2 * _nbytes(o) + 2 * _nbytes(y), 0))
+def ssm_finish(o: torch.Tensor, xbc: torch.Tensor, z: torch.Tensor, skip: torch.Tensor,
+               w: torch.Tensor, y: torch.Tensor, inner: int, value_dim: int, parts: int,
+               eps: float) -> torch.Tensor:
+    """y = (o + skip_h x) * silu(z), divided by its root mean square in ``parts`` equal parts
+    of a row, times ``w``.  ``o`` 32-bit ``[rows, inner]``; x the first ``inner`` columns of
+    the 32-bit ``xbc``; ``z`` a view ``[rows, inner]`` in y's type."""
+    rows = y.shape[0]
+    _f32(o, rows * inner, "o")
+    _want(xbc, torch.float32, "xbc")
+    _want(y, y.dtype, "y")
+    _want(z, y.dtype, "z", contiguous=False)
+    _f32(skip, inner // value_dim, "skip")
+    _f32(w, inner, "w")
+    if tuple(z.shape) != (rows, inner) or z.stride(1) != 1 or tuple(y.shape) != (rows, inner):
+        raise KernelError("ssm_finish: one gate value per output")
+    _check(library().sib_ssm_finish(
+        _ptr(o), _ptr(xbc), c_longlong(xbc.stride(0)), _ptr(z), c_longlong(z.stride(0)), _ptr(skip),
+        _ptr(w), _ptr(y), _code(y.dtype), c_int(rows), c_int(inner), c_int(value_dim), c_int(parts),
+        c_float(eps), _stream()))
+    return y
+
+
+@_timed(lambda proj, a_col, decay_in, w0, a_bias, prep, *a: ("general_delta_prepare", _nbytes(proj, prep), 0))
+def gdelta_prepare(proj: torch.Tensor, a_col: int, decay_in: torch.Tensor, w0: torch.Tensor,
+                   a_bias: torch.Tensor, prep: torch.Tensor, n_heads: int, dim: int) -> torch.Tensor:
+    """First step of the generalized delta rule (csrc/general_delta.cu): from projected rows
+    ``[r | k | v | ...]`` with the removal rates' inputs at column ``a_col`` and the decays'
+    inputs ``decay_in`` the six 32-bit vectors per row and head that the recurrence reads:
+    r | k | w | u | a u | v (``prep`` ``[rows, heads, 6, dim]``)."""
+    rows = proj.shape[0]
+    n = n_heads * dim
+    _want(proj, proj.dtype, "proj")
+    _want(decay_in, proj.dtype, "decay_in", contiguous=False)
+    if proj.shape[1] < max(3 * n, a_col + n) or tuple(decay_in.shape) != (rows, n) or decay_in.stride(1) != 1:
+        raise KernelError("general_delta_prepare: the projected rows do not hold r, k, v and a")
+    _f32(w0, n, "w0")
+    _f32(a_bias, n, "a_bias")
+    _f32(prep, rows * n * 6, "prep")
+    _check(library().sib_gdelta_prepare(
+        _ptr(proj), c_longlong(proj.stride(0)), c_longlong(a_col), _ptr(decay_in),
+        c_longlong(decay_in.stride(0)), _code(proj.dtype), _ptr(w0), _ptr(a_bias), _ptr(prep),
+        c_int(rows), c_int(n_heads), c_int(dim), _stream()))
+    return prep
+
+
+@_timed(lambda prep, state, out, ctx, n_heads, dim: (
+    "general_delta_scan", 2 * ctx.n_seqs * n_heads * dim * dim * 4 + _nbytes(prep, out),
+    8.0 * out.shape[0] * n_heads * dim * dim))
+def gdelta_scan(prep: torch.Tensor, state: torch.Tensor, out: torch.Tensor, ctx, n_heads: int,
+                dim: int) -> torch.Tensor:
+    """The generalized delta rule over the step's rows, sequence by sequence, from and into the
+    slots' matrices ``state[slot, :heads * dim * dim]``; ``out`` 32-bit ``[rows, heads * dim]``."""
+    rows = out.shape[0]
+    _want(state, torch.float32, "state")
+    _f32(prep, rows * n_heads * 6 * dim, "prep")
+    _f32(out, rows * n_heads * dim, "out")
+    if state.shape[1] < n_heads * dim * dim:
+        raise KernelError("general_delta_scan: the state is too small for the matrices")
+    _check(library().sib_gdelta_scan(
+        _ptr(prep), _ptr(state), c_longlong(state.stride(0)), _ptr(out), _ptr(ctx.seq_slot),
+        _ptr(ctx.seq_start), _ptr(ctx.seq_end), _ptr(ctx.seq_row0), c_int(rows), c_int(ctx.n_seqs),
+        c_int(n_heads), c_int(dim), _stream()))
+    return out
+
+
 def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits: int) -> int:
     return int(library().sib_attention_rows_scratch_bytes(c_int(rows), c_int(n_heads),
                                                           c_int(head_dim), c_int(splits)))
@@ -833,7 +1106,7 @@ def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits:
 
 @_timed(lambda q, q_stride, k_new, v_new, kv_stride, k_pool, v_pool, page_table, page_tokens,
         ring_tokens, row_pos, row_seq, seq_slot, seq_start, seq_row0, out, scratch, n_heads, n_kv,
-        head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False: (
+        head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False, cells=None: (
             _attention_cache_work("attention_rows (cache)", row_pos, k_pool, n_heads, head_dim,
                                   window, out.shape[0]) if k_pool is not None else
             ("attention_rows (prompt)", 2 * _nbytes(out) * (1 + 2 * n_kv / n_heads),
@@ -845,10 +1118,13 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
                    row_pos, row_seq, seq_slot, seq_start, seq_row0, out: torch.Tensor,
                    scratch: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                    scale: float, softcap: float, window: int, splits: int,
-                   sink: Optional[torch.Tensor] = None, values_in_keys: bool = False) -> torch.Tensor:
+                   sink: Optional[torch.Tensor] = None, values_in_keys: bool = False,
+                   cells=None) -> torch.Tensor:
     """General attention of independent rows (see csrc/attention_rows.cu).  ``sink``: one
     32-bit value per query head whose exponential joins the softmax's denominator.
     ``values_in_keys``: a value is its key's cell (``v_new`` / ``v_pool`` are not read).
+    ``cells``: a cache view (``KVView``) with cells of pooled blocks; a row then also sees
+    the blocks that lie wholly before its window, one key and one value each.
 
     ``q``, ``k_new``, ``v_new`` may be views into one packed buffer; only
     their first elements' addresses and the strides are used."""
@@ -871,7 +1147,13 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
         _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_row0), _ptr(out),
         _ptr(scratch), _code(out.dtype), c_int(rows), c_int(n_heads), c_int(n_kv), c_int(head_dim),
         c_float(scale), c_float(softcap), c_int(window), c_int(splits), _ptr(sink),
-        c_int(1 if values_in_keys else 0), _stream()))
+        c_int(1 if values_in_keys else 0),
+        _ptr(cells.cell_k if cells is not None else None),
+        _ptr(cells.cell_v if cells is not None else None),
+        _ptr(cells.cell_table if cells is not None else None),
+        c_int(cells.need.pool if cells is not None else 0),
+        c_int(cells.cell_table.shape[1] if cells is not None else 0),
+        c_int(cells.cell_page_tokens if cells is not None else 0), _stream()))
     return out
 
 

@@ -2,6 +2,7 @@
 built-in parts."""
 
 from . import registry  # noqa: F401
-from . import norm, position, attention, recurrent, feed_forward, block, embedding  # noqa: F401
+from . import norm, position, attention, recurrent, feed_forward, block, embedding, pair  # noqa: F401
 from .registry import (register_block, register_embedding, register_feed_forward,  # noqa: F401
-                       register_head, register_mixer, register_norm, register_position)
+                       register_head, register_mixer, register_norm, register_position,
+                       register_tail)

@@ -42,6 +42,15 @@ the projection and the attention kernel, in 32-bit):
                 are the ones cached.
 ``head_gate``   each head's output is multiplied by sigmoid(g_h), g = ``g_proj.weight`` x
                 (one number per head, from the mixer's input), before the output product.
+``pool``        P > 0 (with a ``window``): beside the window's tokens a row sees one key and one
+                value for every block of P positions (bP .. bP + P - 1) that lies wholly before
+                its window (bP + P - 1 <= position - window): the means of the block's keys
+                and values as the cache holds them.  Tokens and blocks share one softmax.
+                The cache keeps a cell per block (``KVNeed.pool``), written by the step that
+                brings the block's last position (csrc/head_prepare.cu pool_store).
+
+Worked-on heads (any of the options above) are rotated in half-split or neighbouring pairs,
+as the position part says, and are attended to by the general kernel when a window is set.
 """
 
 from __future__ import annotations
@@ -116,7 +125,7 @@ class Attention:
     def _extras(params: Mapping) -> bool:
         """Whether the heads are worked on between the projection and the attention."""
         return bool(params.get("bias") or params.get("qk_norm") or params.get("value_mix")
-                    or params.get("head_gate")
+                    or params.get("head_gate") or params.get("pool")
                     or int(params.get("value_dim") or params["head_dim"]) != params["head_dim"])
 
     @staticmethod
@@ -200,9 +209,11 @@ class Attention:
         pos: PartSpec = params["position"]
         pos_w = {k[len("position."):]: v for k, v in weights.items() if k.startswith("position.")}
         self.position = part_class("position", pos.kind)(pos.params, self.hd, pos_w, rt)
+        self.pool = int(params.get("pool") or 0)
+        if self.pool < 0 or (self.pool and self.window <= 0):
+            raise ConfigError("attention: pooled blocks go with a window")
+        self.rope_style = native.ROPE_HALF_SPLIT
         if self.extras:
-            if self.window:
-                raise ConfigError("attention: a window together with worked-on heads is not built")
             norm = params.get("qk_norm")
             self.qk_eps = float(norm["eps"]) if norm else 0.0
             self.bias = weights.get("qkv_proj.bias")
@@ -214,9 +225,9 @@ class Attention:
             self.head_gate = bool(params.get("head_gate"))
             self.n_qkv = (self.nh + self.nkv) * self.hd + self.nkv * self.vd
             rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
-            if rotary is None or rotary[2] != native.ROPE_HALF_SPLIT:
-                raise ConfigError("attention: worked-on heads take a rotary position part with "
-                                  "half-split pairs (or 'none')")
+            if rotary is None:
+                raise ConfigError("attention: worked-on heads take a rotary position part (or 'none')")
+            self.rope_style = rotary[2]
         self.w_qkv = rt.cast_matrix(weights["qkv_proj.weight"])
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
@@ -225,7 +236,7 @@ class Attention:
         self._block_warps = tuple(int(w) for w in os.environ.get("SIB_DECODE_WARPS", "8,4,2").split(","))
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(kv=KVNeed(self.nkv, self.kw, self.window))
+        return CacheNeed(kv=KVNeed(self.nkv, self.kw, self.window, pool=self.pool))
 
     # ------------------------------------------------------------------
     def _longest(self, ctx, capacity: int) -> int:
@@ -333,7 +344,7 @@ class Attention:
         if not fresh and view.ring_tokens > 0 and not ctx.graph_capture:
             # rows that attend over a ring must not overwrite a key that an earlier row of
             # the same step still sees (a captured step adds one position: always fine)
-            room = view.ring_tokens - self.window + 1
+            room = view.ring_tokens - max(self.window, self.pool) + 1
             for start, n in zip(ctx.starts, ctx.counts):
                 if n > room and start + n > view.ring_tokens:
                     raise ValueError(
@@ -358,7 +369,9 @@ class Attention:
                                 rotary[0], rotary[1], v_first, self.lam if v_first is not None else None,
                                 ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, view.k, view.v,
                                 view.page_table, view.page_tokens, view.ring_tokens, nh, nkv,
-                                self.hd, self.vd, hd)
+                                self.hd, self.vd, hd, style=self.rope_style)
+            if self.pool:
+                native.pool_store(qkv, view, ctx, nh, nkv, hd)
             if self.value_mix == "first":
                 ctx.memo["value_mix.first"] = qkv[:, (nh + nkv) * hd:]
         elif (rotary is not None and rotary[1] == hd and rotary[2] == native.ROPE_HALF_SPLIT
@@ -398,7 +411,24 @@ class Attention:
         # 28 against 39 us, 8 of 256 36 against 56 us the other way round)
         short = ctx.max_count <= rt.short_prompt_tokens and native.attention_prefill_supports(
             nh, self.nkv, hd)
-        if fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
+        if self.pool or (self.extras and self.window):
+            # blocks before the window join the softmax: the general kernel, which reads the
+            # step's own keys from the packed rows, earlier ones from the cache and the blocks'
+            # cells from their store
+            cached = not fresh
+            splits = self._splits(ctx, ctx.cache.max_seq_len) if cached else 1
+            scratch = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+            native.attention_rows(qkv, width, None if cached else qkv[:, nh * hd:],
+                                  None if cached else qkv[:, (nh + nkv) * hd:], width,
+                                  view.k if cached else None, view.v if cached else None,
+                                  view.page_table if cached else None, view.page_tokens,
+                                  view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
+                                  ctx.seq_start, ctx.seq_row0, out, scratch, nh, self.nkv, hd,
+                                  self.scale, self.softcap, self.window, splits,
+                                  cells=view if self.pool else None)
+        elif fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
                 not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
             # a launch too small for the device splits its long blocks, given the memory
             # (with the lengths known on the host, not in a recorded step, the launch is a

@@ -16,6 +16,15 @@ add are RMS norms the block runs "norm of the sub-layer's output, add, norm
 for the next sub-layer" as one kernel (csrc/norm.cu add_rms_norm), reaching
 over to the next block's first norm when the model passes it; Dynamic Tanh norms around an
 add are fused in the same way (add_dyt_norm).
+
+``parallel`` (one norm, both sub-layers read its output, one add):
+
+    n = pre_mixer(h);   h += mixer(n) + feed_forward(n)
+
+A block may carry a *tail* (a registered "tail" part, such as ``token_side``): it runs behind
+the sub-layers on the stream itself, and its output passes an RMS norm with the tail's own
+weight before it is added: y = tail(h); h += y / rms(y) * tail.gain.  That norm, the add and
+the next block's first norm are one launch of the residual kernel.
 """
 
 from __future__ import annotations
@@ -118,3 +127,65 @@ class PreNormBlock(SandwichBlock):
 
 register_block("sandwich", SandwichBlock)
 register_block("pre_norm", PreNormBlock)
+
+
+class ParallelBlock:
+    norm_sites = ("pre_mixer",)
+
+    def __init__(self, mixer, feed_forward, norms: Mapping[str, object], rt, tail=None):
+        if norms.get("pre_mixer") is None:
+            raise ConfigError("block: the 'pre_mixer' norm is required")
+        self.mixer = mixer
+        self.feed_forward = feed_forward       # None: the layer is its mixer alone
+        self.pre_mixer = norms["pre_mixer"]
+        self.tail = tail
+        self.rt = rt
+
+    @property
+    def first_norm(self):
+        return self.pre_mixer
+
+    chain_safe = False
+
+    @property
+    def captures_prompts(self) -> bool:
+        return all(p is None or getattr(p, "captures_prompts", False)
+                   for p in (self.mixer, self.feed_forward, self.tail)) and self.mixer is not None
+
+    def _add(self, y: torch.Tensor, post, h: torch.Tensor, nxt, want_rows: bool = False):
+        """h += y (normed by ``post``'s gain if given); returns nxt(h), or h's rows as
+        activations when ``want_rows``, or None."""
+        out = torch.empty_like(y) if (nxt is not None or want_rows) else None
+        if _fusable(nxt):
+            self.rt.add_rms_norm(y, post.gain if post is not None else None,
+                                 post.eps if post is not None else 0.0, h,
+                                 nxt.gain if nxt is not None else None,
+                                 nxt.eps if nxt is not None else 0.0, out)
+            return out
+        self.rt.add_rms_norm(y, post.gain if post is not None else None,
+                             post.eps if post is not None else 0.0, h, None, 0.0, None)
+        return nxt.forward(h, out_dtype=self.rt.dtype)
+
+    def forward(self, h: torch.Tensor, normed: Optional[torch.Tensor], ctx, entry: int,
+                cache_entry: int, owns_cache: bool, next_norm=None) -> Optional[torch.Tensor]:
+        if normed is None:
+            self.rt.flush()
+            normed = self.pre_mixer.forward(h, out_dtype=self.rt.dtype)
+        a = self.mixer.forward(normed, ctx, entry, cache_entry, owns_cache)
+        f = self.feed_forward.forward(normed, ctx) if self.feed_forward is not None else None
+        if self.tail is None:
+            if f is not None:
+                self._add(a, None, h, None)
+                return self._add(f, None, h, next_norm)
+            return self._add(a, None, h, next_norm)
+        # the sums go into the 32-bit stream; the tail reads the stream's rows as activations
+        if f is not None:
+            self._add(a, None, h, None)
+            x = self._add(f, None, h, None, want_rows=True)
+        else:
+            x = self._add(a, None, h, None, want_rows=True)
+        y = self.tail.forward(x, ctx)
+        return self._add(y, self.tail, h, next_norm)
+
+
+register_block("parallel", ParallelBlock)

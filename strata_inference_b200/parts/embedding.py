@@ -1,7 +1,9 @@
 """Token embedding and the output head.
 
 Embedding: row gather, then a multiply by ``scale`` (the 32-bit residual
-stream starts here).  Reference: src/model/layer.rs:1279-1288.
+stream starts here).  Reference: src/model/layer.rs:1279-1288.  With ``side_width`` S > 0
+the token also picks a row of a second table ``side.weight`` ``[vocab, S]``, left for the
+layers as ``ctx.memo["token_side"]`` (32-bit; parts/pair.py ``token_side`` reads its slice).
 
 ``bigram_embedding``: the token's row times ``scale`` plus a row of a second table picked
 by a hash of the previous token and the token, (prev * mul_prev + token * mul_cur) mod
@@ -39,11 +41,17 @@ class TokenEmbedding:
 
     @staticmethod
     def tensors(params: Mapping, hidden: int, vocab: int) -> Dict[str, TensorDecl]:
-        return {"weight": TensorDecl((vocab, hidden))}
+        out = {"weight": TensorDecl((vocab, hidden))}
+        if int(params.get("side_width") or 0) > 0:
+            out["side.weight"] = TensorDecl((vocab, int(params["side_width"])))
+        return out
 
     @staticmethod
     def resident(params: Mapping, hidden: int, vocab: int) -> Dict[str, Resident]:
-        return {"weight": Resident((vocab, hidden), pieces=(Piece("weight"),))}
+        out = {"weight": Resident((vocab, hidden), pieces=(Piece("weight"),))}
+        if int(params.get("side_width") or 0) > 0:
+            out["side.weight"] = Resident((vocab, int(params["side_width"])), pieces=(Piece("side.weight"),))
+        return out
 
     def __init__(self, params: Mapping, hidden: int, vocab: int,
                  weights: Mapping[str, torch.Tensor], rt):
@@ -52,11 +60,16 @@ class TokenEmbedding:
         self.vocab = vocab
         self.scale = float(params.get("scale", 1.0))
         self.table = rt.cast_matrix(weights["weight"])
+        self.side = rt.cast_matrix(weights["side.weight"]) if "side.weight" in weights else None
 
     def forward(self, ctx) -> torch.Tensor:
         """The step's rows of the 32-bit residual stream.  An embedding gets the whole
         step context: one that adds learned positions reads ``ctx.row_pos`` too."""
         tokens = ctx.tokens
+        if self.side is not None:
+            rows = torch.empty((tokens.numel(), self.side.shape[1]), dtype=torch.float32,
+                               device=tokens.device)
+            ctx.memo["token_side"] = native.embed_rows(tokens, self.side, 1.0, rows)
         h = torch.empty((tokens.numel(), self.hidden), dtype=torch.float32, device=tokens.device)
         return native.embed_rows(tokens, self.table, self.scale, h)
 

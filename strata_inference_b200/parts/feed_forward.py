@@ -11,6 +11,17 @@ then writes act(gate) * up directly.
 
 ``mlp``: the feed-forward without a gate, down(act(up(x))), no biases; act is the square of
 relu (``activation``: "relu_squared"), the tanh-GELU or SiLU.
+
+``routed_experts``: many small gated feed-forwards of which every row uses ``top``.  Parameters:
+``experts``, ``top``, ``intermediate_size``, ``limit``, ``alpha`` (default 1.702), ``router_bias``,
+``shared`` (None, or {"intermediate_size", "limit"}: one more expert that every row uses).
+    expert(x) = down(g * sigmoid(alpha g) * (u + 1)),  g = min(gate x, limit),  u = clamp(up x, +-limit)
+    z = router x + bias (32-bit);  the ``top`` largest z choose the experts (ties: the lower index),
+    their weights are the softmax over the chosen z alone;  y = sum_k p_k expert_k(x) + shared(x)
+Few rows, and every recorded step: each (row, expert) pair streams its expert's matrices
+(csrc/routed.cu routed_rows).  Many rows: the pairs are sorted by expert on the device, the
+experts' sizes are read on the host, and every expert that was chosen runs as two library
+products over its rows.
 """
 
 from __future__ import annotations
@@ -24,6 +35,8 @@ from ..kernels import native
 from ..weights.arena import Piece, Resident
 from ..weights.loader import TensorDecl
 from .registry import register_feed_forward
+
+from typing import Optional
 
 # activation of the gate -> (elementwise kernel's code, fused epilogue of the products or None)
 _ACTIVATIONS = {"gelu_pytorch_tanh": (native.ACT_GELU_TANH, native.EPI_GEGLU),
@@ -128,5 +141,119 @@ class PlainMLP:
         return self.rt.linear(up, self.w_down)
 
 
+class RoutedExperts:
+    captures_prompts = True   # a recorded step reads the choices on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        E, top, ff = int(params["experts"]), int(params["top"]), int(params["intermediate_size"])
+        if E <= 0 or not 0 < top <= min(E, 32) or ff <= 0:
+            raise ConfigError(f"routed_experts: {E} experts of {ff}, {top} a row (at most 32)")
+        shared = params.get("shared") or None
+        sff = int(shared["intermediate_size"]) if shared else 0
+        if shared and sff <= 0:
+            raise ConfigError("routed_experts: the shared expert's intermediate_size must be positive")
+        return E, top, ff, sff
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        E, top, ff, sff = cls._sizes(params)
+        out = {"router.weight": TensorDecl((E, hidden))}
+        if params.get("router_bias", True):
+            out["router.bias"] = TensorDecl((E,), init="norm")
+        for e in range(E):
+            out[f"experts.{e}.gate_proj.weight"] = TensorDecl((ff, hidden))
+            out[f"experts.{e}.up_proj.weight"] = TensorDecl((ff, hidden))
+            out[f"experts.{e}.down_proj.weight"] = TensorDecl((hidden, ff))
+        if sff:
+            out["shared.gate_proj.weight"] = TensorDecl((sff, hidden))
+            out["shared.up_proj.weight"] = TensorDecl((sff, hidden))
+            out["shared.down_proj.weight"] = TensorDecl((hidden, sff))
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        """All experts' gate and up matrices as one [experts, 2 ff, hidden] (an expert's gate
+        rows, then its up rows) and their down matrices as one [experts, hidden, ff]; the
+        router's matrix 32-bit."""
+        E, top, ff, sff = cls._sizes(params)
+        gu, down = [], []
+        for e in range(E):
+            gu += [Piece(f"experts.{e}.gate_proj.weight", e * 2 * ff),
+                   Piece(f"experts.{e}.up_proj.weight", e * 2 * ff + ff)]
+            down.append(Piece(f"experts.{e}.down_proj.weight", e * hidden))
+        out = {"router.weight": Resident((E, hidden), torch.float32, (Piece("router.weight"),)),
+               "experts.gate_up.weight": Resident((E * 2 * ff, hidden), pieces=tuple(gu)),
+               "experts.down.weight": Resident((E * hidden, ff), pieces=tuple(down))}
+        if params.get("router_bias", True):
+            out["router.bias"] = Resident((E,), torch.float32, (Piece("router.bias"),))
+        if sff:
+            out["shared.gate_up.weight"] = Resident((2 * sff, hidden), pieces=(
+                Piece("shared.gate_proj.weight", 0), Piece("shared.up_proj.weight", sff)))
+            out["shared.down.weight"] = Resident((hidden, sff), pieces=(Piece("shared.down_proj.weight"),))
+        return out
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.hidden = hidden
+        self.E, self.top, self.ff, self.sff = self._sizes(params)
+        self.limit = float(params["limit"])
+        self.alpha = float(params.get("alpha", 1.702))
+        self.w_router = weights["router.weight"]
+        self.b_router = weights.get("router.bias")
+        self.w_gu = rt.cast_matrix(weights["experts.gate_up.weight"]).view(self.E, 2 * self.ff, hidden)
+        self.w_down = rt.cast_matrix(weights["experts.down.weight"]).view(self.E, hidden, self.ff)
+        self.shared_limit = float(params["shared"]["limit"]) if self.sff else 0.0
+        self.w_sgu = rt.cast_matrix(weights["shared.gate_up.weight"]) if self.sff else None
+        self.w_sdown = rt.cast_matrix(weights["shared.down.weight"]) if self.sff else None
+        # up to this many rows every (row, expert) pair streams its own expert's matrices
+        self.pair_rows = 32
+
+    def choose(self, x: torch.Tensor):
+        """(ids int32 [rows, top], weights 32-bit [rows, top]) of the rows' experts."""
+        R = x.shape[0]
+        x32 = x if x.dtype == torch.float32 else native.cast_rows(
+            x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
+        with native.profile_region("library product (router, 32-bit)", (R + self.E) * self.hidden * 4,
+                                   2.0 * R * self.E * self.hidden):
+            z = torch.matmul(x32, self.w_router.t())
+        ids = torch.empty((R, self.top), dtype=torch.int32, device=x.device)
+        p = torch.empty((R, self.top), dtype=torch.float32, device=x.device)
+        native.router_topk(z, self.b_router, ids, p)
+        return ids, p
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        rt, R = self.rt, x.shape[0]
+        rt.flush()
+        ids, p = self.choose(x)
+        base: Optional[torch.Tensor] = None
+        if self.sff:
+            gu = rt.linear(x, self.w_sgu)
+            mid = torch.empty((R, self.sff), dtype=x.dtype, device=x.device)
+            native.expert_activate(gu, mid, None, self.shared_limit, self.alpha)
+            base = rt.linear(mid, self.w_sdown)
+        out = torch.empty((R, self.hidden), dtype=x.dtype, device=x.device)
+        if ctx.graph_capture or R <= self.pair_rows:
+            return native.routed_rows(x, self.w_gu, self.w_down, ids, p, base, out, self.limit, self.alpha)
+        # the pairs sorted by expert; `where[r, k]`: the sorted place of row r's k-th pair
+        flat = ids.view(-1).to(torch.int64)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=self.E).tolist()
+        where = torch.empty_like(order, dtype=torch.int32)
+        where[order] = torch.arange(order.numel(), dtype=torch.int32, device=x.device)
+        xs = x.index_select(0, torch.div(order, self.top, rounding_mode="floor"))
+        ys = torch.empty((R * self.top, self.hidden), dtype=x.dtype, device=x.device)
+        at = 0
+        for e, n in enumerate(counts):
+            if n:
+                gu = rt.linear(xs[at:at + n], self.w_gu[e])
+                mid = torch.empty((n, self.ff), dtype=x.dtype, device=x.device)
+                native.expert_activate(gu, mid, None, self.limit, self.alpha)
+                ys[at:at + n] = rt.linear(mid, self.w_down[e])
+                at += n
+        return native.routed_combine(ys, where.view(R, self.top), p, base, out)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
 register_feed_forward("mlp", PlainMLP)
+register_feed_forward("routed_experts", RoutedExperts)

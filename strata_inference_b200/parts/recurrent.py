@@ -33,6 +33,24 @@ the recurrence besides the projections (unit norms, decays, gates, the state) is
         q, k rotated by the token's position;  k <- key_scale k
         S <- decay_h S + k v^T;  o = S^T q
     then per head o / rms(o) (no weight), times silu(g_proj x), and o_proj.  State: S.
+
+``state_space``  the selective state-space layer in its dual (matrix) form.  Parameters:
+    ``num_heads`` H, ``value_dim`` P (a head's channels; inner = H P), ``state_dim`` N,
+    ``groups`` G (head h reads B and C of group h // (H / G)), ``conv_taps``, ``norm_groups``,
+    ``norm_eps``.  One product makes z | x | B | C | dt; x, B and C pass a causal convolution
+    per channel with a bias and SiLU;
+        dt = softplus(dt + dt_bias);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x
+    then y * silu(z), divided by its root mean square in ``norm_groups`` equal parts, times
+    norm.weight, and o_proj.  State: S (N x P per head) and the convolution's last
+    ``conv_taps - 1`` inputs.
+
+``general_delta``  the delta rule with a decay and a removal rate per key channel.
+    Parameters: ``num_heads``, ``head_dim`` d (keys, values and the read-out vector alike),
+    ``decay_rank`` (the width of the decay's two-matrix path), ``norm_eps``.
+        w = exp(-e^-1/2 sigmoid(w2 tanh(w1 x) + w0));  a = sigmoid(a_proj x + bias)
+        u = k / sqrt(sum k^2 + 1e-6);  S <- diag(w) S - (a u)(u^T S) + k v^T;  o = S^T r
+    then per head o / rms(o), times norm.weight (one per head and dimension) and
+    sigmoid(g_proj x), and o_proj.  State: S (d x d per head).
 """
 
 from __future__ import annotations
@@ -297,6 +315,176 @@ class Retention:
         return rt.linear(y, self.w_o)
 
 
+class StateSpace:
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        H, P, N = int(params["num_heads"]), int(params["value_dim"]), int(params["state_dim"])
+        G, taps = int(params.get("groups") or 1), int(params["conv_taps"])
+        parts = int(params.get("norm_groups") or 1)
+        if H <= 0 or G <= 0 or H % G:
+            raise ConfigError(f"state_space: {H} heads cannot share {G} groups")
+        if not 0 < N <= 512 or P <= 0 or not 1 <= taps <= 64:
+            raise ConfigError(f"state_space: state_dim {N} (at most 512), value_dim {P}, "
+                              f"{taps} taps (1 to 64)")
+        if parts <= 0 or (H * P) % parts:
+            raise ConfigError(f"state_space: {H * P} channels cannot be normed in {parts} equal parts")
+        return H, P, N, G, taps, parts
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        H, P, N, G, taps, _ = cls._sizes(params)
+        inner, channels = H * P, H * P + 2 * G * N
+        return {
+            "in_proj.weight": TensorDecl((inner + channels + H, hidden)),
+            "conv.weight": TensorDecl((channels, taps), init="norm"),
+            "conv.bias": TensorDecl((channels,), init="norm"),
+            "dt_bias": TensorDecl((H,), init="norm"),
+            "A_log": TensorDecl((H,), init="norm"),
+            "D": TensorDecl((H,), init="norm"),
+            "norm.weight": TensorDecl((inner,), init="norm"),
+            "o_proj.weight": TensorDecl((hidden, inner)),
+        }
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        H, P, N, G, taps, _ = cls._sizes(params)
+        inner, channels = H * P, H * P + 2 * G * N
+        f32 = torch.float32
+        return {
+            "in_proj.weight": Resident((inner + channels + H, hidden), pieces=(Piece("in_proj.weight"),)),
+            "conv.weight": Resident((channels, taps), f32, (Piece("conv.weight"),)),
+            "conv.bias": Resident((channels,), f32, (Piece("conv.bias"),)),
+            "dt_bias": Resident((H,), f32, (Piece("dt_bias"),)),
+            "A_log": Resident((H,), f32, (Piece("A_log"),)),
+            "D": Resident((H,), f32, (Piece("D"),)),
+            "norm.gain": Resident((inner,), f32, (Piece("norm.weight"),)),
+            "o_proj.weight": Resident((hidden, inner), pieces=(Piece("o_proj.weight"),)),
+        }
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.H, self.P, self.N, self.G, self.taps, self.parts = self._sizes(params)
+        self.eps = float(params["norm_eps"])
+        self.inner = self.H * self.P
+        self.channels = self.inner + 2 * self.G * self.N
+        self.matrices = self.H * self.P * self.N       # floats of a slot's state before the history
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self.conv_w, self.conv_b = weights["conv.weight"], weights["conv.bias"]
+        self.a_log, self.dt_bias, self.skip = weights["A_log"], weights["dt_bias"], weights["D"]
+        self.norm_gain = weights["norm.gain"]
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(state=StateNeed((_round4(self.matrices + (self.taps - 1) * self.channels),)))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("state_space: a recurrent state cannot be lent to another run")
+        rt, H, P, N, G = self.rt, self.H, self.P, self.N, self.G
+        R = x.shape[0]
+        state = ctx.state(cache_entry)
+        proj = rt.linear(x, self.w_in)
+        rt.flush()
+        f32 = dict(dtype=torch.float32, device=x.device)
+        xbc = torch.empty((R, self.channels), **f32)
+        keep, take = torch.empty((R, H), **f32), torch.empty((R, H), **f32)
+        native.ssm_prepare(proj, self.conv_w, self.conv_b, self.a_log, self.dt_bias, state,
+                           self.matrices, xbc, keep, take, ctx, H, self.inner, self.channels, self.taps)
+        o = torch.empty((R, self.inner), **f32)
+        native.gated_scan(xbc[:, self.inner + G * N:], xbc[:, self.inner:self.inner + G * N],
+                          xbc[:, :self.inner], keep, take, state, o, ctx, H, G, N, P)
+        y = torch.empty((R, self.inner), dtype=proj.dtype, device=x.device)
+        native.ssm_finish(o, xbc, proj[:, :self.inner], self.skip, self.norm_gain, y, self.inner, P,
+                          self.parts, self.eps)
+        return rt.linear(y, self.w_o)
+
+
+class GeneralDelta:
+    captures_prompts = True      # sequences, slots and counts are read on the device only
+
+    @staticmethod
+    def _sizes(params: Mapping):
+        H, d, rank = int(params["num_heads"]), int(params["head_dim"]), int(params["decay_rank"])
+        if H <= 0 or not 0 < d <= 512 or rank <= 0:
+            raise ConfigError(f"general_delta: {H} heads, head_dim {d} (at most 512), decay_rank {rank}")
+        return H, d, rank
+
+    @classmethod
+    def _in_rows(cls, params: Mapping):
+        H, d, _ = cls._sizes(params)
+        return [("r_proj.weight", H * d), ("k_proj.weight", H * d), ("v_proj.weight", H * d),
+                ("g_proj.weight", H * d), ("a_proj.weight", H * d)]
+
+    @classmethod
+    def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
+        H, d, rank = cls._sizes(params)
+        out = {name: TensorDecl((n, hidden)) for name, n in cls._in_rows(params)}
+        out.update({
+            "a_proj.bias": TensorDecl((H * d,), init="norm"),
+            "w1.weight": TensorDecl((rank, hidden)),
+            "w2.weight": TensorDecl((H * d, rank)),
+            "w0": TensorDecl((H * d,), init="norm"),
+            "norm.weight": TensorDecl((H * d,), init="norm"),
+            "o_proj.weight": TensorDecl((hidden, H * d)),
+        })
+        return out
+
+    @classmethod
+    def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
+        H, d, rank = cls._sizes(params)
+        pieces, n_in = _pieces(cls._in_rows(params))
+        f32 = torch.float32
+        return {
+            "in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+            "w1.weight": Resident((rank, hidden), pieces=(Piece("w1.weight"),)),
+            "w2.weight": Resident((H * d, rank), pieces=(Piece("w2.weight"),)),
+            "a_proj.bias": Resident((H * d,), f32, (Piece("a_proj.bias"),)),
+            "w0": Resident((H * d,), f32, (Piece("w0"),)),
+            "norm.gain": Resident((H * d,), f32, (Piece("norm.weight"),)),
+            "o_proj.weight": Resident((hidden, H * d), pieces=(Piece("o_proj.weight"),)),
+        }
+
+    def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
+        self.rt = rt
+        self.H, self.d, self.rank = self._sizes(params)
+        self.eps = float(params["norm_eps"])
+        self.w_in = rt.cast_matrix(weights["in_proj.weight"])
+        self.w1, self.w2 = rt.cast_matrix(weights["w1.weight"]), rt.cast_matrix(weights["w2.weight"])
+        self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        self.a_bias, self.w0 = weights["a_proj.bias"], weights["w0"]
+        self.norm_gain = weights["norm.gain"]
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(state=StateNeed((_round4(self.H * self.d * self.d),)))
+
+    def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
+                owns_cache: bool) -> torch.Tensor:
+        if not owns_cache:
+            raise ValueError("general_delta: a recurrent state cannot be lent to another run")
+        rt, H, d = self.rt, self.H, self.d
+        R, n = x.shape[0], self.H * self.d
+        state = ctx.state(cache_entry)
+        proj = rt.linear(x, self.w_in)
+        low = rt.linear(x, self.w1)
+        rt.flush()
+        native.activate(low, low, native.ACT_TANH)
+        decay_in = rt.linear(low, self.w2)
+        rt.flush()
+        prep = torch.empty((R, H, 6, d), dtype=torch.float32, device=x.device)
+        native.gdelta_prepare(proj, 4 * n, decay_in, self.w0, self.a_bias, prep, H, d)
+        o = torch.empty((R, n), dtype=torch.float32, device=x.device)
+        native.gdelta_scan(prep, state, o, ctx, H, d)
+        y = torch.empty((R, n), dtype=proj.dtype, device=x.device)
+        native.head_norm_gate(o, None, self.norm_gain, proj[:, 3 * n:4 * n], y, H, d, self.eps,
+                              native.GATE_SIGMOID)
+        return rt.linear(y, self.w_o)
+
+
 register_mixer("gated_delta", GatedDeltaRule)
 register_mixer("retention", Retention)
 register_mixer("matrix_memory", MatrixMemory)
+register_mixer("state_space", StateSpace)
+register_mixer("general_delta", GeneralDelta)

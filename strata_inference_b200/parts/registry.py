@@ -14,7 +14,7 @@ from ..config.spec import ConfigError, PartSpec
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {},
-    "block": {}, "embedding": {}, "head": {}, "joint": {},
+    "block": {}, "embedding": {}, "head": {}, "joint": {}, "tail": {},
 }
 
 
@@ -54,6 +54,12 @@ def register_head(kind: str, cls: type) -> type:
 def register_joint(kind: str, cls: type) -> type:
     """A part that joins two streams into one: ``forward(h, x0) -> h``."""
     return _register("joint", kind, cls)
+
+
+def register_tail(kind: str, cls: type) -> type:
+    """A part that runs behind a layer's sub-layers, on the stream itself: ``forward(x, ctx) -> y``
+    with ``gain`` and ``eps`` of the RMS norm that y passes before it is added."""
+    return _register("tail", kind, cls)
 
 
 def part_class(role: str, kind: str) -> type:
