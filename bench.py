@@ -160,6 +160,8 @@ def kv_bytes_per_step(engine, lengths):
         per_token = 2 * grp.need.n_kv_heads * grp.need.head_dim * grp.k.element_size()
         for n in lengths:
             seen = min(n, grp.need.window) if grp.need.window else n
+            if grp.need.window and getattr(grp.need, "pool", 0):
+                seen += max(0, (n - grp.need.window) // grp.need.pool)      # one cell per block
             total += len(grp.entries) * seen * per_token
     return total
 
@@ -485,6 +487,31 @@ def vavupel_config(size):
             "loop": {"start": 2, "stop": n_layers - 2, "times": 1}, "logit_softcap": 30.0}
 
 
+def gegorax_config(size):
+    """Gegorax at these sizes: attention with pooled blocks beside a state-space layer, two
+    layers of the generalized delta rule, and so on; feed-forwards in turn dense (the other
+    models' width, two matrices) and 32 experts of an eighth of that width of which a row uses
+    4, beside a shared one of half the width (a row's experts together as wide as the dense
+    one); a window of 1 024 with blocks of 64; state-space heads of 64 channels and 128 states
+    over the model's width; delta-rule matrices of 128 x 128; 64 columns a layer from the token."""
+    width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": ff // 8, "limit": 7.0},
+              "shared": {"ff": ff // 2, "limit": 7.0}}
+    pair = {"left": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                     "mask": {"size": 1024, "pool": 64}, "rot": {"base": 10000.0, "dims": hd}},
+            "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+                      "norm_groups": 1}}
+    delta = {"heads": width // 128, "dim": 128, "decay_rank": 64}
+    layers = []
+    for i in range(n_layers):
+        kind = "parallel" if i % 3 == 0 else "general_delta"
+        layers.append({"type": kind, "mixer": pair if kind == "parallel" else delta,
+                       "mlp": routed if i % 2 else dense})
+    return {"architecture": "Gegorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "token_side": {"dim": 64}, "layers": layers}
+
+
 def gemma2_config_like(size):
     width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
     cfg = baseline_config()
@@ -497,6 +524,18 @@ def gemma2_config_like(size):
 def state_bytes_per_step(engine, batch):
     """Bytes of recurrent state a single-token step reads and writes."""
     return sum(2 * batch * t[0].numel() * t.element_size() for t in engine.cache.state.values())
+
+
+def unread_expert_bytes(engine, rows):
+    """Bytes of routed experts that a step of ``rows`` rows cannot read: a row reads the
+    experts it chose, so at most rows x top of a layer's experts are touched."""
+    total = 0
+    for blk in engine.model.blocks:
+        ff = getattr(blk, "feed_forward", None)
+        if hasattr(ff, "w_gu") and hasattr(ff, "top"):
+            per = (ff.w_gu[0].numel() + ff.w_down[0].numel()) * ff.w_gu.element_size()
+            total += max(0, ff.E - rows * ff.top) * per
+    return total
 
 
 def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
@@ -527,8 +566,9 @@ def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
                 # (a model whose logits have a matrix of their own reads a few rows of its
                 # embedding tables in a step, not the tables)
                 weight_bytes -= sum(t.numel() * t.element_size() for t in (
-                    engine.model.embedding.table, getattr(engine.model.embedding, "bigram", None))
-                    if t is not None)
+                    engine.model.embedding.table, getattr(engine.model.embedding, "bigram", None),
+                    getattr(engine.model.embedding, "side", None)) if t is not None)
+                # (of routed experts a row reads the ones it chose: at most rows x top of them)
                 row["weights_read_gb"] = round(weight_bytes / 1e9, 2)
             ms = time_prefill(engine, T)
             row["prefill_2048_ms"] = round(ms, 3)
@@ -536,7 +576,8 @@ def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
             for b in batches:
                 dms, lengths, _, _ = time_decode(engine, b, context, max(8, args.steps // 2),
                                                  args.warmup, 3)
-                moved = weight_bytes + kv_bytes_per_step(engine, lengths) + state_bytes_per_step(engine, b)
+                moved = (weight_bytes - unread_expert_bytes(engine, b) + kv_bytes_per_step(engine, lengths)
+                         + state_bytes_per_step(engine, b))
                 row[f"decode_b{b}_ms"] = round(dms, 4)
                 row[f"decode_b{b}_tok_s"] = round(b * 1e3 / dms, 1)
                 row[f"decode_b{b}_hbm_frac"] = round(moved / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)
@@ -589,8 +630,11 @@ def main():
     ap.add_argument("--vavupel", action="store_true",
                     help="instead of the timed run: Vavupel beside Karupel at equal layer sizes "
                          "(--size; with --kernels also the per-kernel tables of both)")
+    ap.add_argument("--gegorax", action="store_true",
+                    help="instead of the timed run: Gegorax beside Karupel at equal layer sizes "
+                         "(--size; with --kernels also the per-kernel tables of both)")
     ap.add_argument("--size", default="", choices=[""] + sorted(KARUPEL_SIZES),
-                    help="with --karupel or --vavupel: one of the sizes (default: all)")
+                    help="with --karupel, --vavupel or --gegorax: one of the sizes (default: all)")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -608,6 +652,9 @@ def main():
     if args.vavupel:
         return run_karupel(args, (("vavupel", vavupel_config), ("karupel", karupel_config)),
                            "Vavupel beside Karupel")
+    if args.gegorax:
+        return run_karupel(args, (("gegorax", gegorax_config), ("karupel", karupel_config)),
+                           "Gegorax beside Karupel")
     if args.karupel:
         return run_karupel(args)
     if args.kernels:
