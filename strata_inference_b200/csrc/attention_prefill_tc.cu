@@ -284,6 +284,10 @@ struct TcArgs {
     int window;
     float scale, softcap;
     const float* sink;       // [n_heads] or null: e^{sink_h} joins each row's denominator
+    // [rows, n_heads, head_dim + 2] or null: per (row, head) the (max, sum, accumulator) of keys
+    // that another kernel has summed (scaled scores, natural exponentials), joined with this
+    // kernel's own before the last division: pooled blocks before the window
+    const float* extra;
 };
 
 // SPLIT.  When the grid is small against the device, a block (or pair) of query rows with
@@ -689,8 +693,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
             // a sink: one more term of the denominator, with no key and no value (too large a
             // one gives an infinite sum and therefore a row of zeros, which is its limit)
             if (p.sink != nullptr && l_all > 0.f) l_all += exp2_fast(p.sink[head] * LOG2E - base);
-            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             const bool store = pos < n && pos >= q0;
+            // another kernel's partial result for this row and head
+            float w_own = 1.f, w_extra = 0.f;
+            const float* extra = nullptr;
+            if (p.extra != nullptr && store) {
+                const float* ex = p.extra + ((size_t)(row0 + pos) * p.n_heads + head) * (HD + 2);
+                const float l_x = __ldg(ex + 1);
+                if (l_x > 0.f) {
+                    const float m_x = __ldg(ex) * LOG2E;
+                    const float top = fmaxf(base, m_x);
+                    w_own = l_all > 0.f ? exp2_fast(base - top) : 0.f;
+                    w_extra = exp2_fast(m_x - top);
+                    l_all = w_own * l_all + w_extra * l_x;
+                    extra = ex + 2;
+                }
+            }
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(row0 + pos) * p.n_heads * HD + (size_t)head * HD +
                                  (HD / 2) * half;
 #pragma unroll 1
@@ -703,6 +722,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map, TcArgs p,
                     for (int j = 0; j < 32; ++j)
                         o[j] = __float_as_uint(w_mine * __uint_as_float(o[j]) +
                                                w_theirs * __ldcg(theirs + (size_t)(col0 + j) * BM + row));
+                }
+                if (extra != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        o[j] = __float_as_uint(w_own * __uint_as_float(o[j]) + w_extra * __ldg(extra + col0 + j));
                 }
                 if (store) {
 #pragma unroll
@@ -1031,9 +1055,11 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
                                         float scale, float softcap, int window, void* scratch,
                                         long long scratch_bytes, int* tickets, int n_tickets,
                                         const int* host_lens, const int* seq_q0, const int* host_q0,
-                                        const float* sink, void* stream) {
+                                        const float* sink, const float* extra, void* stream) {
     if (n_seqs == 0 || max_len == 0) return 0;
     SIB_REQUIRE(sink == nullptr || softcap == 0.f, "attention_prefill_tc: a sink together with a cap is not built");
+    SIB_REQUIRE(extra == nullptr || (softcap == 0.f && sink == nullptr && ((uintptr_t)extra % 4) == 0),
+                "attention_prefill_tc: another kernel's partial results go with no cap and no sink");
     SIB_REQUIRE(sib_attention_prefill_tc_supports(n_heads, n_kv, head_dim, width),
                 "attention_prefill_tc: heads=%d kv_heads=%d head_dim=%d is not a shape this kernel "
                 "takes (1 or 2 heads per kv head; head_dim 64, 128 or 256)", n_heads, n_kv, head_dim);
@@ -1090,7 +1116,7 @@ SIB_EXPORT int sib_attention_prefill_tc(const void* qkv, int width, int total_ro
     }
     if (items.n > 0) split_tiles = 0;
     TcArgs p{(__nv_bfloat16*)out, seq_row0, seq_len, seq_q0, error_flag, (float*)scratch, tickets,
-             split_tiles, n_heads, n_kv, window, scale, softcap, sink};
+             split_tiles, n_heads, n_kv, window, scale, softcap, sink, extra};
     cudaStream_t s = (cudaStream_t)stream;
 #define BY_G(HD, PAIR)                                                         \
     do {                                                                       \

@@ -15,7 +15,9 @@
 // With pooled blocks (`pool` > 0, a window and a second cache of one cell per block of `pool`
 // positions): beside the window's keys the row sees block b's cell if the block's last
 // position is at or before p - window, i.e. the first (p - window + 1) / pool blocks; cells
-// and keys share the one softmax.  The row's keys are then numbered blocks first.
+// and keys share the one softmax.  The row's keys are then numbered blocks first.  With
+// `cells_only` the kernel stops before the window and leaves each (row, head)'s partial result
+// (max, sum, accumulator over its blocks) for the prompt kernel of the tensor cores to join.
 // Keys at positions >= seq_start[b] (this step's own rows) are read from the
 // step's packed k/v rows when those are given; earlier ones from the cache.
 // With splits > 1 each (row, head) is cut into `splits` runs of keys whose
@@ -54,6 +56,9 @@ struct AttnRowsArgs {
     const void* pv_pool;
     const int* pool_table;
     int pool, pool_max_pages, pool_page_tokens;
+    // 1: the blocks alone (no window): every (row, head) leaves its (max, sum, accumulator) in
+    // `partial` as one split would, for another kernel to join with the window's
+    int cells_only;
 };
 
 template <typename T> struct Vec16;
@@ -118,10 +123,11 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
     const int row0 = p.seq_row0[b];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int nb = p.pk_pool && p.window > 0 && slot >= 0 ? max(0, pos - p.window + 1) / p.pool : 0;
-    const int n = nb + pos - lo + 1;           // keys are numbered lo - nb .. pos: blocks first
+    const int last = p.cells_only ? lo - 1 : pos;
+    const int n = nb + last - lo + 1;          // keys are numbered lo - nb .. pos: blocks first
     const int chunk = (n + p.splits - 1) / p.splits;
     const int j0 = lo - nb + split * chunk;
-    const int j1 = min(j0 + chunk, pos + 1);
+    const int j1 = min(j0 + chunk, last + 1);
 
     bool live[NI];
     float qv[NI][V], acc[NI][V];
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
         }
     }
 
-    if (p.splits == 1) {
+    if (p.splits == 1 && !p.cells_only) {
         if (p.sink) {       // one more term of the denominator
             const float sk = p.sink[h];
             const float mx = fmaxf(m, sk);
@@ -355,8 +361,11 @@ SIB_EXPORT int sib_attention_rows(
     const int* seq_start, const int* seq_row0, void* out, float* partial, int dtype, int rows,
     int n_heads, int n_kv, int head_dim, float scale, float softcap, int window, int splits,
     const float* sink, int values_in_keys, const void* pk_pool, const void* pv_pool,
-    const int* pool_table, int pool, int pool_max_pages, int pool_page_tokens, void* stream) {
+    const int* pool_table, int pool, int pool_max_pages, int pool_page_tokens, int cells_only,
+    void* stream) {
     if (rows == 0) return 0;
+    SIB_REQUIRE(!cells_only || (pk_pool != nullptr && partial != nullptr && splits == 1 && sink == nullptr),
+                "attention_rows: the blocks alone need their cache, room for the results and one split");
     SIB_REQUIRE(rows > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0,
                 "attention_rows: rows=%d heads=%d kv_heads=%d", rows, n_heads, n_kv);
     SIB_REQUIRE(pk_pool == nullptr || (pv_pool && pool_table && pool > 0 && pool_max_pages > 0 &&
@@ -384,7 +393,7 @@ SIB_EXPORT int sib_attention_rows(
                    seq_start, seq_row0, page_table, q_stride, kv_stride, rows, n_heads, n_kv,
                    head_dim, max_pages, page_tokens, ring_tokens, window, splits, scale, softcap,
                    sink, values_in_keys, pk_pool, pv_pool, pool_table, pool, pool_max_pages,
-                   pool_page_tokens};
+                   pool_page_tokens, cells_only};
     const long long units = (long long)rows * n_heads * splits;
     const long long blocks = (units + 3) / 4;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_rows: too many rows (%d)", rows);
@@ -401,7 +410,7 @@ SIB_EXPORT int sib_attention_rows(
     });
 #undef LAUNCH
     int rc = sib_check_launch("attention_rows");
-    if (rc || splits == 1) return rc;
+    if (rc || splits == 1 || cells_only) return rc;
     const CombineShape c = combine_shape(splits, head_dim);
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(attention_combine_kernel<T>, dim3(rows * n_heads),
                                                  dim3(c.threads), c.smem, s, partial, (T*)out,

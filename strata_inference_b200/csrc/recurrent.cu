@@ -743,31 +743,29 @@ SIB_EXPORT int sib_ssm_prepare(const void* proj, long long stride, int dtype, co
     return sib_check_launch("conv_history");
 }
 
-// One warp per (row, part of the row).
+// One block per (row, part of the row).
 template <typename T>
 __global__ void __launch_bounds__(128)
 ssm_finish_kernel(const float* __restrict__ o, const float* __restrict__ xbc, long long x_stride,
                   const T* __restrict__ z, long long z_stride, const float* __restrict__ skip,
                   const float* __restrict__ w, T* __restrict__ y, int rows, int inner, int vd,
                   int parts, float eps) {
+    __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (unit >= (long long)rows * parts) return;
-    const size_t r = unit / parts;
-    const int part = (int)(unit % parts), len = inner / parts, e0 = part * len;
+    const size_t r = blockIdx.x / parts;
+    const int part = (int)(blockIdx.x % parts), len = inner / parts, e0 = part * len;
     auto value = [&](int e) {
         const float zz = to_f32(z[r * z_stride + e]);
         return (o[r * inner + e] + skip[e / vd] * xbc[r * x_stride + e]) * silu_f(zz);
     };
     float ss = 0.f;
-    for (int e = e0 + lane; e < e0 + len; e += 32) {
+    for (int e = e0 + threadIdx.x; e < e0 + len; e += blockDim.x) {
         const float v = value(e);
         ss += v * v;
     }
-    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)len + eps);
-    for (int e = e0 + lane; e < e0 + len; e += 32)
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)len + eps);
+    for (int e = e0 + threadIdx.x; e < e0 + len; e += blockDim.x)
         y[r * inner + e] = from_f32<T>(value(e) * inv * w[e]);
 }
 
@@ -778,7 +776,7 @@ SIB_EXPORT int sib_ssm_finish(const float* o, const float* xbc, long long x_stri
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && inner > 0 && vd > 0 && inner % vd == 0 && parts > 0 && inner % parts == 0,
                 "ssm_finish: rows=%d inner=%d head width=%d parts=%d", rows, inner, vd, parts);
-    const long long blocks = ((long long)rows * parts + 3) / 4;
+    const long long blocks = (long long)rows * parts;
     SIB_REQUIRE(blocks < (1ll << 31), "ssm_finish: too many rows (%d)", rows);
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(ssm_finish_kernel<T>, dim3((unsigned)blocks), dim3(128),
                                                  0, (cudaStream_t)stream, o, xbc, x_stride,

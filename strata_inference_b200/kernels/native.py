@@ -523,6 +523,26 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.T
                                      c_int(experts), c_int(top), _stream()))
 
 
+@_timed(lambda x, w, bias, ids, weights: ("router_rows", _nbytes(x, w), 2.0 * x.shape[0] * w.numel()))
+def router_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
+                weights: torch.Tensor) -> None:
+    """Few rows: z = w x (+ ``bias``) with the 32-bit matrix ``w`` ``[experts, width]`` and the
+    choice of :func:`router_topk`, in one launch; sums are 32-bit."""
+    rows, width = x.shape
+    experts, top = w.shape[0], ids.shape[1]
+    _want(x, x.dtype, "x", contiguous=False)
+    _want(w, torch.float32, "w")
+    _want(ids, torch.int32, "ids")
+    _f32(weights, rows * top, "weights")
+    if bias is not None:
+        _f32(bias, experts, "bias")
+    if w.shape[1] != width or ids.shape[0] != rows or x.stride(1) != 1:
+        raise KernelError("router_rows: shapes do not fit")
+    _check(library().sib_router_rows(_ptr(x), c_longlong(x.stride(0)), _code(x.dtype), _ptr(w), _ptr(bias),
+                                     _ptr(ids), _ptr(weights), c_int(rows), c_int(width),
+                                     c_int(experts), c_int(top), _stream()))
+
+
 @_timed(lambda gu, y, row_weight, limit, alpha: ("expert_activate", _nbytes(gu, y), 0))
 def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torch.Tensor],
                     limit: float, alpha: float) -> torch.Tensor:
@@ -541,15 +561,20 @@ def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torc
     return y
 
 
+_PAIR_ORDER: dict = {}
+
+
 @_timed(lambda x, w_gu, w_down, ids, weights, base, out, limit, alpha: (
-    "routed_rows", ids.numel() * 3 * w_down.shape[1] * w_down.shape[2] * x.element_size(),
+    "routed_rows", min(ids.numel(), w_down.shape[0]) * 3 * w_down.shape[1] * w_down.shape[2] * x.element_size(),
     6.0 * ids.numel() * w_down.shape[1] * w_down.shape[2]))
 def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                 weights: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor,
                 limit: float, alpha: float) -> torch.Tensor:
     """The chosen experts of every row, each (row, expert) pair streaming its expert's matrices
     (csrc/routed.cu): ``w_gu`` ``[experts, 2 ff, width]`` (gate rows, then up rows), ``w_down``
-    ``[experts, width, ff]``; out = base + sum_k weights[r, k] down(act(gate, up)) in 32-bit."""
+    ``[experts, width, ff]``; out = base + sum_k weights[r, k] down(act(gate, up)) in 32-bit.
+    With more pairs than half the experts the kernels go expert by expert instead (an expert's
+    matrices are read once for all the pairs that chose it)."""
     rows, width = x.shape
     top = ids.shape[1]
     experts, _, ff = w_down.shape
@@ -564,6 +589,18 @@ def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: 
     if base is not None:
         _want(base, x.dtype, "base")
     mid = torch.empty((rows * top, ff), dtype=x.dtype, device=x.device)
+    pairs = rows * top
+    if 2 * pairs > experts and (max(width, ff) + 4 + pairs) * 4 <= 48 * 1024:
+        # more pairs than half the experts: expert-major, an expert's matrices read once
+        order = _PAIR_ORDER.get((pairs, x.device))
+        if order is None:
+            order = _PAIR_ORDER[(pairs, x.device)] = torch.arange(pairs, dtype=torch.int32, device=x.device)
+        ys = torch.empty((pairs, width), dtype=x.dtype, device=x.device)
+        _check(library().sib_routed_by_expert(
+            _ptr(x), c_longlong(x.stride(0)), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
+            _ptr(base), _ptr(mid), _ptr(ys), _ptr(order), _ptr(out), _code(x.dtype), c_int(rows),
+            c_int(width), c_int(ff), c_int(top), c_int(experts), c_float(limit), c_float(alpha), _stream()))
+        return out
     _check(library().sib_routed_rows(
         _ptr(x), c_longlong(x.stride(0)), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
         _ptr(base), _ptr(mid), _ptr(out), _code(x.dtype), c_int(rows), c_int(width), c_int(ff),
@@ -1106,7 +1143,9 @@ def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits:
 
 @_timed(lambda q, q_stride, k_new, v_new, kv_stride, k_pool, v_pool, page_table, page_tokens,
         ring_tokens, row_pos, row_seq, seq_slot, seq_start, seq_row0, out, scratch, n_heads, n_kv,
-        head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False, cells=None: (
+        head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False, cells=None,
+        cells_only=False: (
+            ("attention_rows (blocks)", _nbytes(out), 0) if cells_only else
             _attention_cache_work("attention_rows (cache)", row_pos, k_pool, n_heads, head_dim,
                                   window, out.shape[0]) if k_pool is not None else
             ("attention_rows (prompt)", 2 * _nbytes(out) * (1 + 2 * n_kv / n_heads),
@@ -1119,7 +1158,7 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
                    scratch: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                    scale: float, softcap: float, window: int, splits: int,
                    sink: Optional[torch.Tensor] = None, values_in_keys: bool = False,
-                   cells=None) -> torch.Tensor:
+                   cells=None, cells_only: bool = False) -> torch.Tensor:
     """General attention of independent rows (see csrc/attention_rows.cu).  ``sink``: one
     32-bit value per query head whose exponential joins the softmax's denominator.
     ``values_in_keys``: a value is its key's cell (``v_new`` / ``v_pool`` are not read).
@@ -1141,6 +1180,10 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
             raise KernelError(f"attention_rows: {need} bytes of scratch memory are needed")
     if sink is not None:
         _f32(sink, n_heads, "sink")
+    if cells_only:
+        if cells is None or splits != 1:
+            raise KernelError("attention_rows: the blocks alone need their cache and one split")
+        _f32(scratch, rows * n_heads * (head_dim + 2), "scratch")
     _check(library().sib_attention_rows(
         _ptr(q), c_int(q_stride), _ptr(k_new), _ptr(v_new), c_int(kv_stride), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens),
@@ -1153,7 +1196,8 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
         _ptr(cells.cell_table if cells is not None else None),
         c_int(cells.need.pool if cells is not None else 0),
         c_int(cells.cell_table.shape[1] if cells is not None else 0),
-        c_int(cells.cell_page_tokens if cells is not None else 0), _stream()))
+        c_int(cells.cell_page_tokens if cells is not None else 0),
+        c_int(1 if cells_only else 0), _stream()))
     return out
 
 
@@ -1320,7 +1364,7 @@ def attention_prefill_tc_plan(lens: Sequence[int], n_heads: int, n_kv: int, head
 
 @_timed(lambda qkv, out, seq_row0, seq_len, n_seqs, max_len, n_heads, n_kv, head_dim, scale,
         softcap, window, scratch=None, tickets=None, host_lens=None, seq_q0=None,
-        host_q0=None, sink=None: _prompt_work(
+        host_q0=None, sink=None, extra=None: _prompt_work(
             "attention_prefill_tc (tcgen05)", qkv, seq_len, n_heads, head_dim, window))
 def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len, n_seqs: int,
                          max_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
@@ -1329,9 +1373,13 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
                          host_lens: Optional[Sequence[int]] = None,
                          seq_q0: Optional[torch.Tensor] = None,
                          host_q0: Optional[Sequence[int]] = None,
-                         sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         sink: Optional[torch.Tensor] = None,
+                         extra: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The prompt attention on tcgen05 (see csrc/attention_prefill_tc.cu).  ``sink``: one 32-bit
-    value per head whose exponential joins every row's denominator (no cap then).  With ``scratch``
+    value per head whose exponential joins every row's denominator (no cap then).  ``extra``:
+    32-bit ``[rows, heads, head_dim + 2]``, per row and head the (max, sum, accumulator) of keys
+    that another kernel has summed (``attention_rows`` with ``cells_only``), joined with this
+    kernel's own sums before the last division (no cap, no sink then).  With ``scratch``
     and ``tickets`` (int32, zero before the first call; every call leaves them zero) of the
     sizes ``attention_prefill_tc_split`` gives, a launch that cannot fill the device runs its
     long blocks of query rows as two halves.  With ``host_lens`` (the prompts' lengths, as
@@ -1348,6 +1396,8 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         _want(tickets, torch.int32, "tickets")
     if sink is not None:
         _f32(sink, n_heads, "sink")
+    if extra is not None:
+        _f32(extra, qkv.shape[0] * n_heads * (head_dim + 2), "extra")
     _check(library().sib_attention_prefill_tc(
         _ptr(qkv), c_int(qkv.shape[1]), c_int(qkv.shape[0]), _ptr(out), _ptr(seq_row0),
         _ptr(seq_len), c_int(n_seqs), c_int(max_len), c_int(n_heads), c_int(n_kv), c_int(head_dim),
@@ -1357,7 +1407,7 @@ def attention_prefill_tc(qkv: torch.Tensor, out: torch.Tensor, seq_row0, seq_len
         None if host_lens is None else (c_int * len(host_lens))(*[int(n) for n in host_lens]),
         _ptr(seq_q0),
         None if host_q0 is None else (c_int * len(host_q0))(*[int(n) for n in host_q0]),
-        _ptr(sink), _stream()))
+        _ptr(sink), _ptr(extra), _stream()))
     return out
 
 

@@ -411,7 +411,10 @@ class Attention:
         # 28 against 39 us, 8 of 256 36 against 56 us the other way round)
         short = ctx.max_count <= rt.short_prompt_tokens and native.attention_prefill_supports(
             nh, self.nkv, hd)
-        if self.pool or (self.extras and self.window):
+        tc_prompt = (fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0
+                     and not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width)
+                     and not (self.pool and self.softcap))
+        if (self.pool or (self.extras and self.window)) and not tc_prompt:
             # blocks before the window join the softmax: the general kernel, which reads the
             # step's own keys from the packed rows, earlier ones from the cache and the blocks'
             # cells from their store
@@ -428,8 +431,17 @@ class Attention:
                                   ctx.seq_start, ctx.seq_row0, out, scratch, nh, self.nkv, hd,
                                   self.scale, self.softcap, self.window, splits,
                                   cells=view if self.pool else None)
-        elif fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0 and \
-                not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width):
+        elif tc_prompt:
+            extra = None
+            if self.pool:
+                # the blocks before each row's window first, by the general kernel: (max, sum,
+                # accumulator) per row and head, which the prompt kernel joins with its own
+                extra = torch.empty((R, nh, hd + 2), dtype=torch.float32, device=qkv.device)
+                native.attention_rows(qkv, width, qkv[:, nh * hd:], qkv[:, (nh + nkv) * hd:], width,
+                                      None, None, None, view.page_tokens, view.ring_tokens,
+                                      ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_start,
+                                      ctx.seq_row0, out, extra, nh, self.nkv, hd, self.scale, 0.0,
+                                      self.window, 1, cells=view, cells_only=True)
             # a launch too small for the device splits its long blocks, given the memory
             # (with the lengths known on the host, not in a recorded step, the launch is a
             # balanced list of work items)
@@ -445,7 +457,7 @@ class Attention:
             native.attention_prefill_tc(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,
                                         ctx.max_count, nh, self.nkv, hd, self.scale, self.softcap,
                                         self.window, rt.scratch(need) if need else None,
-                                        rt.tickets(n_tickets) if need else None, lens)
+                                        rt.tickets(n_tickets) if need else None, lens, extra=extra)
         elif fresh and qkv.dtype == torch.bfloat16 and \
                 native.attention_prefill_supports(nh, self.nkv, hd):
             native.attention_prefill(qkv, out, ctx.seq_row0, ctx.seq_end, ctx.n_seqs,

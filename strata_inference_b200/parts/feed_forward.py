@@ -19,9 +19,9 @@ relu (``activation``: "relu_squared"), the tanh-GELU or SiLU.
     z = router x + bias (32-bit);  the ``top`` largest z choose the experts (ties: the lower index),
     their weights are the softmax over the chosen z alone;  y = sum_k p_k expert_k(x) + shared(x)
 Few rows, and every recorded step: each (row, expert) pair streams its expert's matrices
-(csrc/routed.cu routed_rows).  Many rows: the pairs are sorted by expert on the device, the
-experts' sizes are read on the host, and every expert that was chosen runs as two library
-products over its rows.
+(csrc/routed.cu routed_rows).  Many rows: the pairs are sorted by expert on the device into a
+layout [experts, most rows of any expert, width] (that one number is read on the host) and all
+experts run as two batched library products around one activation launch.
 """
 
 from __future__ import annotations
@@ -143,6 +143,7 @@ class PlainMLP:
 
 class RoutedExperts:
     captures_prompts = True   # a recorded step reads the choices on the device only
+    reads_sizes_on_host = True   # a launched step of many rows reads how many rows chose each expert
 
     @staticmethod
     def _sizes(params: Mapping):
@@ -212,6 +213,11 @@ class RoutedExperts:
     def choose(self, x: torch.Tensor):
         """(ids int32 [rows, top], weights 32-bit [rows, top]) of the rows' experts."""
         R = x.shape[0]
+        if R <= self.pair_rows and (self.hidden + self.E + 4) * 4 <= 48 * 1024:
+            ids = torch.empty((R, self.top), dtype=torch.int32, device=x.device)
+            p = torch.empty((R, self.top), dtype=torch.float32, device=x.device)
+            native.router_rows(x, self.w_router, self.b_router, ids, p)
+            return ids, p
         x32 = x if x.dtype == torch.float32 else native.cast_rows(
             x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
         with native.profile_region("library product (router, 32-bit)", (R + self.E) * self.hidden * 4,
@@ -235,23 +241,36 @@ class RoutedExperts:
         out = torch.empty((R, self.hidden), dtype=x.dtype, device=x.device)
         if ctx.graph_capture or R <= self.pair_rows:
             return native.routed_rows(x, self.w_gu, self.w_down, ids, p, base, out, self.limit, self.alpha)
-        # the pairs sorted by expert; `where[r, k]`: the sorted place of row r's k-th pair
+        # The pairs sorted by expert and laid out [experts, most, width] with `most` the largest
+        # number of rows any expert got (the one number read on the host; rows behind an
+        # expert's own are zeros): all experts run as ONE batched library product for gate and
+        # up, one activation launch and one batched product for down.  `where[r, k]`: the
+        # place of row r's k-th pair in that layout.
+        E, top, W = self.E, self.top, self.hidden
         flat = ids.view(-1).to(torch.int64)
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=self.E).tolist()
-        where = torch.empty_like(order, dtype=torch.int32)
-        where[order] = torch.arange(order.numel(), dtype=torch.int32, device=x.device)
-        xs = x.index_select(0, torch.div(order, self.top, rounding_mode="floor"))
-        ys = torch.empty((R * self.top, self.hidden), dtype=x.dtype, device=x.device)
-        at = 0
-        for e, n in enumerate(counts):
-            if n:
-                gu = rt.linear(xs[at:at + n], self.w_gu[e])
-                mid = torch.empty((n, self.ff), dtype=x.dtype, device=x.device)
-                native.expert_activate(gu, mid, None, self.limit, self.alpha)
-                ys[at:at + n] = rt.linear(mid, self.w_down[e])
-                at += n
-        return native.routed_combine(ys, where.view(R, self.top), p, base, out)
+        counts = torch.bincount(flat, minlength=E)
+        most = int(counts.max().item())
+        most = -(-most // 8) * 8
+        by_expert = flat[order]
+        place = by_expert * most + (torch.arange(order.numel(), device=x.device)
+                                    - (torch.cumsum(counts, 0) - counts)[by_expert])
+        xs = torch.zeros((E * most, W), dtype=x.dtype, device=x.device)
+        xs.index_copy_(0, place, x.index_select(0, torch.div(order, top, rounding_mode="floor")))
+        where = torch.empty(order.numel(), dtype=torch.int32, device=x.device)
+        where[order] = place.to(torch.int32)
+        esz = x.element_size()
+        with native.profile_region(f"library product (experts, {E} x {most} rows, gate and up)",
+                                   (E * most * (W + 2 * self.ff) + self.w_gu.numel()) * esz,
+                                   2.0 * E * most * W * 2 * self.ff):
+            gu = torch.bmm(xs.view(E, most, W), self.w_gu.transpose(1, 2))
+        mid = torch.empty((E * most, self.ff), dtype=x.dtype, device=x.device)
+        native.expert_activate(gu.view(E * most, 2 * self.ff), mid, None, self.limit, self.alpha)
+        with native.profile_region(f"library product (experts, {E} x {most} rows, down)",
+                                   (E * most * (W + self.ff) + self.w_down.numel()) * esz,
+                                   2.0 * E * most * W * self.ff):
+            ys = torch.bmm(mid.view(E, most, self.ff), self.w_down.transpose(1, 2))
+        return native.routed_combine(ys.view(E * most, W), where.view(R, top), p, base, out)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

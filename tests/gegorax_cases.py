@@ -226,6 +226,11 @@ BLOCKS = {
     "blocks_of_four": blocks_model(9, 4),          # more than 64 blocks: a second page of cells
     "blocks_of_one": blocks_model(5, 1),
 }
+# heads of 64 and of 128 (values wider than keys): bfloat16 prompts take the tensor cores
+BLOCKS_TC = {
+    "blocks_heads_of_64": blocks_model(20, 8, dim=64, vdim=64, scale=0.1),
+    "blocks_values_of_128": blocks_model(70, 12, heads=1, dim=64, vdim=128, scale=0.1),
+}
 
 
 def tie_queries_to_keys(weights: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:

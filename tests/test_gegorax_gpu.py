@@ -19,7 +19,7 @@ import pytest
 import torch
 
 import plain_gegorax as plain
-from gegorax_cases import (ALONE, BLOCKS, MIXED, NARROW, ODD, SHARP, WIDE, assert_close, asking_prompt,
+from gegorax_cases import (ALONE, BLOCKS, BLOCKS_TC, MIXED, NARROW, ODD, SHARP, WIDE, assert_close, asking_prompt,
                            plain_logits, prompts, random_weights, rows_that_differ, shifted_blocks,
                            tie_queries_to_keys)
 
@@ -374,8 +374,10 @@ def test_router_choice_alone(experts, top):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows, width, ff, experts, top", [(1, 64, 24, 6, 2), (8, 72, 9, 3, 1), (20, 128, 64, 16, 4),
-                                                          (3, 100, 14, 4, 4)])
+                                                          (3, 100, 14, 4, 4), (2, 64, 32, 16, 3), (5, 256, 40, 64, 4),
+                                                          (64, 128, 48, 8, 2)])
 def test_streamed_experts_alone(rows, width, ff, experts, top, dtype):
+    """(pair by pair while the pairs are fewer than half the experts, expert by expert beyond)"""
     from strata_inference_b200.kernels import native
     g = torch.Generator().manual_seed(rows + width)
     rnd = lambda *s: (torch.randn(s, generator=g) * 0.5).to(torch.bfloat16).float()  # noqa: E731
@@ -506,3 +508,98 @@ def test_command_line_generates_from_a_model_folder(tmp_path):
     for k, tok in enumerate(tokens):
         row = logits[len(prompt) + k - 1]
         assert (row.max() - row[tok]).item() <= 1e-4 * row.abs().max().item()
+
+
+@pytest.mark.parametrize("heads, kv, hd, window, pool, lens", [(2, 2, 64, 40, 8, [300, 70, 9]), (4, 2, 128, 130, 16, [520, 200]),
+                                                               (2, 1, 256, 17, 5, [150]), (2, 2, 64, 8, 24, [260, 131])])
+def test_prompt_kernel_joins_the_blocks_before_the_window(heads, kv, hd, window, pool, lens):
+    """The tensor cores' prompt kernel over the window, joined with the general kernel's sums
+    over the blocks before it, against a 64-bit softmax over both: scores spread widely, so a
+    block often carries a row; the general kernel alone over the same rows and cells as well."""
+    from types import SimpleNamespace
+    from strata_inference_b200.kernels import native
+    g = torch.Generator().manual_seed(heads * 1000 + hd + window)
+    scale = 3.0 / math.sqrt(hd)
+    cpt, per_seq = 16, 4                      # cells a page, pages of cells a sequence
+    n_seqs = len(lens)
+    order = torch.randperm(n_seqs * per_seq, generator=g).view(n_seqs, per_seq)
+    cell_k = torch.zeros((n_seqs * per_seq, kv, cpt, hd), dtype=torch.bfloat16)
+    cell_v = torch.zeros_like(cell_k)
+    rows, refs, with_blocks = [], [], 0
+    for b, T in enumerate(lens):
+        q = torch.randn((T, heads, hd), generator=g).to(torch.bfloat16)
+        k = torch.randn((T, kv, hd), generator=g).to(torch.bfloat16)
+        v = torch.randn((T, kv, hd), generator=g).to(torch.bfloat16)
+        nb = T // pool
+        ck = k[:nb * pool].float().view(nb, pool, kv, hd).mean(1).to(torch.bfloat16)
+        cv = v[:nb * pool].float().view(nb, pool, kv, hd).mean(1).to(torch.bfloat16)
+        for c in range(nb):
+            cell_k[order[b, c // cpt], :, c % cpt] = ck[c]
+            cell_v[order[b, c // cpt], :, c % cpt] = cv[c]
+        ref = torch.zeros((T, heads, hd), dtype=torch.float64)
+        for i in range(T):
+            lo, seen = max(0, i - window + 1), max(0, (i - window + 1) // pool)
+            with_blocks += seen > 0
+            for h in range(heads):
+                kk = torch.cat([ck[:seen, h // (heads // kv)], k[lo:i + 1, h // (heads // kv)]]).double()
+                vv = torch.cat([cv[:seen, h // (heads // kv)], v[lo:i + 1, h // (heads // kv)]]).double()
+                ref[i, h] = torch.softmax(kk @ q[i, h].double() * scale, dim=0) @ vv
+        refs.append(ref.view(T, -1))
+        rows.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+    assert with_blocks > sum(lens) // 2
+    packed, ref = torch.cat(rows).contiguous().cuda(), torch.cat(refs)
+    R, width = packed.shape
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    row0 = [sum(lens[:b]) for b in range(n_seqs)]
+    cells = SimpleNamespace(cell_k=cell_k.cuda(), cell_v=cell_v.cuda(), cell_table=order.to(torch.int32).cuda(),
+                            need=SimpleNamespace(pool=pool), cell_page_tokens=cpt)
+    pos, seq = i32([i for T in lens for i in range(T)]), i32([b for b, T in enumerate(lens) for _ in range(T)])
+    slot, start = i32(list(range(n_seqs))), i32([0] * n_seqs)
+
+    def general(out, scratch, only):
+        return native.attention_rows(packed, width, packed[:, heads * hd:], packed[:, (heads + kv) * hd:], width,
+                                     None, None, None, 64, 0, pos, seq, slot, start, i32(row0), out, scratch,
+                                     heads, kv, hd, scale, 0.0, window, 1, cells=cells, cells_only=only)
+    out = general(torch.empty((R, heads * hd), dtype=torch.bfloat16, device="cuda"), None, False)
+    err = (out.cpu().double() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item(), f"general kernel: {err:.3e}"
+    extra = torch.full((R, heads, hd + 2), float("nan"), dtype=torch.float32, device="cuda")
+    general(out, extra, True)
+    assert torch.isfinite(extra[:, :, 1:]).all()
+    out = torch.full((R, heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    native.attention_prefill_tc(packed, out, i32(row0), i32(lens), n_seqs, max(lens), heads, kv, hd, scale, 0.0,
+                                window, extra=extra)
+    assert native.attention_prefill_tc_error() == 0
+    err = (out.cpu().double() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item(), f"prompt kernel with the blocks joined: {err:.3e}"
+    n_items, need, n_tickets = native.attention_prefill_tc_plan(lens, heads, kv, hd, window)
+    if n_items:
+        out.fill_(float("nan"))
+        native.attention_prefill_tc(packed, out, i32(row0), i32(lens), n_seqs, max(lens), heads, kv, hd, scale, 0.0,
+                                    window, torch.empty(max(need, 16), dtype=torch.uint8, device="cuda"),
+                                    torch.zeros(max(n_tickets, 1), dtype=torch.int32, device="cuda"), lens, extra=extra)
+        assert native.attention_prefill_tc_error() == 0
+        err = (out.cpu().double() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item(), f"as a list of work: {err:.3e}"
+
+
+@pytest.mark.parametrize("name", sorted(BLOCKS_TC))
+def test_long_prompts_on_the_tensor_cores_and_through_the_general_kernel_agree(name):
+    from strata_inference_b200.parts import attention
+    cfg = BLOCKS_TC[name]
+    w = tie_queries_to_keys(random_weights(cfg, seed=41))
+    a, b = asking_prompt(cfg, 300, seed=42), asking_prompt(cfg, 190, seed=43)
+    ref = torch.cat([plain_logits(cfg, w, a), plain_logits(cfg, w, b)])
+    got = {}
+    for tc in (True, False):
+        attention._USE_TCGEN05_PREFILL = tc
+        try:
+            eng = make_engine(cfg, w, "bfloat16")
+            sa, sb = eng.new_sequence(), eng.new_sequence()
+            got[tc] = eng.step([(sa, a), (sb, b)], [all_rows(300), all_rows(190)]).cpu().double()
+        finally:
+            attention._USE_TCGEN05_PREFILL = True
+        assert_close(got[tc], ref, "bfloat16", f"{name}, tensor cores: {tc}")
+    diff = (got[True] - got[False]).abs().amax(-1) / ref.abs().max()
+    assert diff.median().item() <= 1.5e-2 and (diff > 4e-2).float().mean().item() <= 0.1, \
+        f"median {diff.median().item():.3e}, worst {diff.max().item():.3e}"
