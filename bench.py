@@ -585,10 +585,11 @@ def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
             print(f"{name} {size}: {json.dumps(row)}", file=sys.stderr, flush=True)
             if args.kernels:
                 pk = load_peaks()
-                slots = [engine.new_sequence() for _ in range(8)]
+                kb = max(1, args.batch)
+                slots = [engine.new_sequence() for _ in range(kb)]
                 fill_context(engine, slots, context - 16)
-                rows, tms = profile_decode_graph(engine, slots, [5] * 8)
-                print(format_table(f"{name} {size}: captured decode step, batch 8, {context - 16} "
+                rows, tms = profile_decode_graph(engine, slots, [5] * kb)
+                print(format_table(f"{name} {size}: captured decode step, batch {kb}, {context - 16} "
                                    f"positions each", rows, tms, pk))
                 for s in slots:
                     engine.end_sequence(s)

@@ -85,7 +85,7 @@ struct GDeltaScanArgs {
 
 constexpr int kPerLane = 16;
 constexpr int kThreads = 64;
-constexpr int kChunk = 8;
+constexpr int kChunkMany = 8;
 
 template <int L> __device__ __forceinline__ float lanes_sum(float v) {
 #pragma unroll
@@ -106,8 +106,11 @@ __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_grou
 
 // kThreads threads = kThreads / L columns side by side; grid (column tiles, heads, sequences).
 // Lane s of a column owns the rows ((i * L + s) * 4 .. + 3), i = 0..3.
-template <int L, bool VEC>
+// kChunk tokens are staged at a time; a step of single tokens stages one (CH = 1: an eighth of
+// the shared memory, so that many more blocks are resident while the states stream through).
+template <int L, bool VEC, int CH>
 __global__ void __launch_bounds__(kThreads) gdelta_scan_kernel(GDeltaScanArgs p) {
+    constexpr int kChunk = CH;
     constexpr int KP = kPerLane * L;            // key width as staged (zeros behind d)
     constexpr int CB = kThreads / L;            // columns of a block
     constexpr int BUF = kChunk * 6 * KP;
@@ -121,7 +124,8 @@ __global__ void __launch_bounds__(kThreads) gdelta_scan_kernel(GDeltaScanArgs p)
     const int slot = p.seq_slot[b];
     const int row0 = p.seq_row0[b], n = p.seq_end[b] - p.seq_start[b];
     const int n_chunks = (n + kChunk - 1) / kChunk;
-    for (int i = tid; i < 2 * BUF; i += kThreads) staged[i] = 0.f;
+    if (d < KP)      // what lies behind the width stays zero: copies only ever write below d
+        for (int i = tid; i < 2 * BUF; i += kThreads) staged[i] = 0.f;
     float* mine = slot >= 0 && col < d
         ? p.state + (size_t)slot * p.state_stride + ((size_t)h * d + col) * d : nullptr;
     pdl_wait();
@@ -155,18 +159,25 @@ __global__ void __launch_bounds__(kThreads) gdelta_scan_kernel(GDeltaScanArgs p)
         __syncthreads();
         if (c + 1 < n_chunks) fetch(staged + ((c + 1) & 1) * BUF, c + 1);
         const int count = min(kChunk, n - c * kChunk);
-        for (int t = 0; t < count; ++t) {
-            const float* v6 = buf + t * 6 * KP;
+        // <u, S_j> of a token is taken right after the token before it has changed the column,
+        // together with that token's <S_j, r>: two sums over the same registers whose
+        // exchanges between the lanes travel side by side (the same additions in the same
+        // order as one after the other)
+        auto along = [&](const float* v6) {
             float su[4] = {0.f, 0.f, 0.f, 0.f};
-            float uu[kPerLane];
 #pragma unroll
             for (int i = 0; i < kPerLane / 4; ++i) {
                 const float4 x = *reinterpret_cast<const float4*>(v6 + 3 * KP + (i * L + s) * 4);
-                uu[4 * i] = x.x; uu[4 * i + 1] = x.y; uu[4 * i + 2] = x.z; uu[4 * i + 3] = x.w;
+                su[0] += S[4 * i] * x.x;
+                su[1] += S[4 * i + 1] * x.y;
+                su[2] += S[4 * i + 2] * x.z;
+                su[3] += S[4 * i + 3] * x.w;
             }
-#pragma unroll
-            for (int i = 0; i < kPerLane; ++i) su[i & 3] += S[i] * uu[i];
-            const float c1 = lanes_sum<L>((su[0] + su[1]) + (su[2] + su[3]));
+            return (su[0] + su[1]) + (su[2] + su[3]);
+        };
+        float c1 = lanes_sum<L>(along(buf));
+        auto token = [&](int t, bool more) {
+            const float* v6 = buf + t * 6 * KP;
             const float vj = col < d ? v6[5 * KP + col] : 0.f;
             float so[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -185,9 +196,22 @@ __global__ void __launch_bounds__(kThreads) gdelta_scan_kernel(GDeltaScanArgs p)
                 so[2] += S[4 * i + 2] * rr.z;
                 so[3] += S[4 * i + 3] * rr.w;
             }
-            const float o = lanes_sum<L>((so[0] + so[1]) + (so[2] + so[3]));
+            float o = (so[0] + so[1]) + (so[2] + so[3]);
+            float next = more ? along(v6 + 6 * KP) : 0.f;
+#pragma unroll
+            for (int w = L / 2; w > 0; w >>= 1) {
+                o += __shfl_xor_sync(0xffffffffu, o, w);
+                next += __shfl_xor_sync(0xffffffffu, next, w);
+            }
+            c1 = next;
             if (s == 0 && col < d)
                 p.out[((size_t)(row0 + c * kChunk + t) * p.H + h) * d + col] = o;
+        };
+        if (count == kChunk) {
+#pragma unroll
+            for (int t = 0; t < kChunk; ++t) token(t, t + 1 < kChunk);
+        } else {
+            for (int t = 0; t < count; ++t) token(t, t + 1 < count);
         }
     }
     if (mine) {
@@ -229,21 +253,25 @@ SIB_EXPORT int sib_gdelta_scan(const float* prep, float* state, long long state_
     const int per_block = kThreads / L;
     const dim3 grid((d + per_block - 1) / per_block, H, n_seqs);
     const bool vec = d % 4 == 0 && ((uintptr_t)prep % 16) == 0;
-    const size_t smem = (size_t)2 * kChunk * 6 * kPerLane * L * sizeof(float);
+    // no sequence of the step has more than one token if there are no more rows than sequences
+    const bool single = rows <= n_seqs;
+    const size_t smem = (size_t)2 * (single ? 1 : kChunkMany) * 6 * kPerLane * L * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-#define GO_ONE(LL, VV)                                                                         \
+#define GO_ONE(LL, VV, CC)                                                                     \
     do {                                                                                       \
         if (smem > 48 * 1024) {                                                                \
-            cudaError_t e = cudaFuncSetAttribute(gdelta_scan_kernel<LL, VV>,                   \
+            cudaError_t e = cudaFuncSetAttribute(gdelta_scan_kernel<LL, VV, CC>,               \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             SIB_REQUIRE(e == cudaSuccess, "general_delta_scan: %s", cudaGetErrorString(e));    \
         }                                                                                      \
-        sib_launch_chained(gdelta_scan_kernel<LL, VV>, grid, dim3(kThreads), smem, s, p);      \
+        sib_launch_chained(gdelta_scan_kernel<LL, VV, CC>, grid, dim3(kThreads), smem, s, p);  \
     } while (0)
-#define GO(LL)                     \
-    do {                           \
-        if (vec) GO_ONE(LL, true); \
-        else GO_ONE(LL, false);    \
+#define GO(LL)                                        \
+    do {                                              \
+        if (vec && single) GO_ONE(LL, true, 1);       \
+        else if (vec) GO_ONE(LL, true, kChunkMany);   \
+        else if (single) GO_ONE(LL, false, 1);        \
+        else GO_ONE(LL, false, kChunkMany);           \
     } while (0)
     if (L == 1) GO(1);
     else if (L == 2) GO(2);

@@ -57,7 +57,9 @@ def profile_decode_graph(engine, slots, tokens, replays: int = 3) -> Tuple[List[
     from .graph import DecodeGraph
     g = DecodeGraph(engine, len(slots), 0.0, 0, 1.0)
     with native.KernelProfile() as eager:
-        g.run(slots, tokens, use_graph=False)
+        # (the first call of a step that will be recorded runs it launched, under the rules
+        # of a recording: the same kernels in the same order as the recording below)
+        g.run(slots, tokens, use_graph=True)
     n = len(eager.events)
     with native.KernelProfile(plan=eager) as captured:
         g.run(slots, tokens, use_graph=True)          # runs once more eagerly, then captures
