@@ -375,7 +375,8 @@ def test_router_choice_alone(experts, top):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows, width, ff, experts, top", [(1, 64, 24, 6, 2), (8, 72, 9, 3, 1), (20, 128, 64, 16, 4),
                                                           (3, 100, 14, 4, 4), (2, 64, 32, 16, 3), (5, 256, 40, 64, 4),
-                                                          (64, 128, 48, 8, 2)])
+                                                          (64, 128, 48, 8, 2), (12, 100, 14, 16, 4),
+                                                          (9, 72, 9, 6, 1), (40, 136, 20, 5, 3)])
 def test_streamed_experts_alone(rows, width, ff, experts, top, dtype):
     """(pair by pair while the pairs are fewer than half the experts, expert by expert beyond)"""
     from strata_inference_b200.kernels import native
