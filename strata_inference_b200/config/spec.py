@@ -60,6 +60,8 @@ class LayerSpec:
     # a registered "tail": a part that runs behind the sub-layers on the stream itself
     # (``names["tail"]`` is what follows the layer's prefix in its tensors' names)
     tail: Optional[PartSpec] = None
+    # parameters of the block arrangement itself (``residual_scale`` of the pre-norm block)
+    block_params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -6,6 +6,7 @@
 // (key/value head g = h / (n_heads / n_kv)):
 //     s_j = scale * <q_h, k_{g,j}>;  if cap > 0: s_j = cap * tanh(s_j / cap)
 //     visible j: max(0, p - window + 1) <= j <= p   (window 0: all j <= p)
+//     with `chunk` > 0 instead: p - p % chunk <= j <= p   (the row's own chunk of positions)
 //     o = sum_j softmax(s)_j v_{g,j}
 // With a sink (one number per query head) the softmax's denominator has one more term,
 // e^{sink_h}: a weight that belongs to no key and no value.  With `values_in_keys` a value
@@ -47,6 +48,7 @@ struct AttnRowsArgs {
     int rows, n_heads, n_kv, head_dim;
     int max_pages, page_tokens, ring_tokens;
     int window, splits;
+    int chunk;              // > 0: a row sees its own chunk of positions (first_visible)
     float scale, softcap;
     const float* sink;      // [n_heads] or null
     int values_in_keys;
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnRowsArgs p) {
     const int slot = p.seq_slot[b];
     const int start = p.seq_start[b];
     const int row0 = p.seq_row0[b];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = first_visible(pos, p.window, p.chunk);
     const int nb = p.pk_pool && p.window > 0 && slot >= 0 ? max(0, pos - p.window + 1) / p.pool : 0;
     const int last = p.cells_only ? lo - 1 : pos;
     const int n = nb + last - lo + 1;          // keys are numbered lo - nb .. pos: blocks first
@@ -359,8 +361,8 @@ SIB_EXPORT int sib_attention_rows(
     const void* k_pool, const void* v_pool, const int* page_table, int max_pages, int page_tokens,
     int ring_tokens, const int* row_pos, const int* row_seq, const int* seq_slot,
     const int* seq_start, const int* seq_row0, void* out, float* partial, int dtype, int rows,
-    int n_heads, int n_kv, int head_dim, float scale, float softcap, int window, int splits,
-    const float* sink, int values_in_keys, const void* pk_pool, const void* pv_pool,
+    int n_heads, int n_kv, int head_dim, float scale, float softcap, int window, int chunk,
+    int splits, const float* sink, int values_in_keys, const void* pk_pool, const void* pv_pool,
     const int* pool_table, int pool, int pool_max_pages, int pool_page_tokens, int cells_only,
     void* stream) {
     if (rows == 0) return 0;
@@ -381,8 +383,9 @@ SIB_EXPORT int sib_attention_rows(
     SIB_REQUIRE(k_new != nullptr || k_pool != nullptr, "attention_rows: no keys given");
     SIB_REQUIRE(k_pool == nullptr || (page_table && page_tokens > 0 && max_pages > 0),
                 "attention_rows: incomplete cache description");
-    SIB_REQUIRE(window >= 0 && ring_tokens >= 0, "attention_rows: window=%d ring=%d", window,
-                ring_tokens);
+    SIB_REQUIRE(window >= 0 && ring_tokens >= 0 && chunk >= 0 && (chunk == 0 || (window == 0 && !pk_pool)),
+                "attention_rows: window=%d ring=%d chunk=%d (a chunk goes without a window)", window,
+                ring_tokens, chunk);
     const int esz = dtype == SIB_F32 ? 4 : 2;
     SIB_REQUIRE(((size_t)q_stride * esz) % 16 == 0 && ((size_t)kv_stride * esz) % 16 == 0 &&
                     ((uintptr_t)q % 16) == 0 && ((uintptr_t)k_new % 16) == 0 &&
@@ -391,7 +394,7 @@ SIB_EXPORT int sib_attention_rows(
                 "attention_rows: rows must start on 16-byte boundaries");
     AttnRowsArgs p{q, k_new, v_new, k_pool, v_pool, out, partial, row_pos, row_seq, seq_slot,
                    seq_start, seq_row0, page_table, q_stride, kv_stride, rows, n_heads, n_kv,
-                   head_dim, max_pages, page_tokens, ring_tokens, window, splits, scale, softcap,
+                   head_dim, max_pages, page_tokens, ring_tokens, window, splits, chunk, scale, softcap,
                    sink, values_in_keys, pk_pool, pv_pool, pool_table, pool, pool_max_pages,
                    pool_page_tokens, cells_only};
     const long long units = (long long)rows * n_heads * splits;

@@ -96,6 +96,15 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// The first position that a row at position `pos` sees, in every attention kernel.  A chunk
+// of `chunk` positions (> 0): the start of the row's own chunk, chunks counted from the
+// sequence's position 0.  Else a sliding window of `window` positions (> 0), the row's own
+// included.  Both 0: position 0.
+__host__ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    if (chunk > 0) return pos - pos % chunk;
+    return window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
+}
+
 // Sum over a block of up to 1024 threads; every thread gets the result.
 // `scratch` holds 33 floats of shared memory and may be reused after return.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

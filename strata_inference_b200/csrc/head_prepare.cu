@@ -312,6 +312,10 @@ struct LatentPrepareArgs {
     int rows, n_heads, qd, rd, rank, pad, rot;
     int max_pages, page_tokens, ring_tokens;
     float eps;
+    // the down projection's rows (rank + rd) where they do not follow the query heads in `proj`
+    // (queries that come from a product of their own); null: they do
+    const void* down;
+    long long down_stride;
 };
 
 template <typename T>
@@ -367,7 +371,8 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(LatentPrepareArgs p
             dst = (T*)p.k_pool + ((size_t)page * p.page_tokens + cell % p.page_tokens) * p.pad;
         }
     }
-    const T* down = row + (size_t)p.n_heads * (p.qd + p.rd);
+    const T* down = p.down ? (const T*)p.down + (size_t)r * p.down_stride
+                           : row + (size_t)p.n_heads * (p.qd + p.rd);
     float ss = 0.f;
     for (int d = lane; d < p.rank; d += 32) {
         const float x = to_f32(down[d]);
@@ -390,7 +395,7 @@ SIB_EXPORT int sib_latent_prepare(
     const float* c_gain, float eps, const float* inv_freq, int rot, const int* row_pos,
     const int* row_seq, const int* seq_slot, const int* seq_end, void* k_pool, const int* page_table,
     int max_pages, int page_tokens, int ring_tokens, int rows, int n_heads, int qd, int rd, int rank,
-    int pad, void* stream) {
+    int pad, const void* down, long long down_stride, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && n_heads > 0 && qd > 0 && rd >= 0 && rank > 0 && pad >= rank + rd,
                 "latent_prepare: rows=%d heads=%d widths %d + %d, rank %d in rows of %d", rows, n_heads,
@@ -405,7 +410,7 @@ SIB_EXPORT int sib_latent_prepare(
     SIB_REQUIRE((n_heads + 4) / 4 < 65536, "latent_prepare: too many heads (%d)", n_heads);
     LatentPrepareArgs p{proj, q_lat, q_rows, k_rows, c_gain, rot ? inv_freq : nullptr, row_pos, row_seq,
                         seq_slot, seq_end, k_pool, page_table, proj_stride, rows, n_heads, qd, rd, rank,
-                        pad, rot, max_pages, page_tokens, ring_tokens, eps};
+                        pad, rot, max_pages, page_tokens, ring_tokens, eps, down, down_stride};
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(latent_prepare_kernel<T>, dim3(rows, (n_heads + 4) / 4),
                                                  dim3(128), 0, (cudaStream_t)stream, p));
     return sib_check_launch("latent_prepare");

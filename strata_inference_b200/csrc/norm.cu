@@ -10,17 +10,18 @@
 #include "common.cuh"
 
 // out[i, :] = rms(x[rows ? rows[i] : i, :], gain).  The row is held in shared
-// memory (hidden floats) between the two passes.
+// memory (hidden floats) between the two passes.  A row of x starts every `x_stride`
+// elements (the leading columns of a wider buffer are normed where it exceeds `hidden`).
 template <typename Tin, typename Tout>
 __global__ void rms_norm_kernel(const Tin* __restrict__ x, const int* __restrict__ rows,
                                 const float* __restrict__ gain, Tout* __restrict__ out,
-                                int hidden, float eps) {
+                                int hidden, float eps, long long x_stride) {
     extern __shared__ float row[];
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
     const int i = blockIdx.x;
-    const Tin* src = x + (size_t)(rows ? rows[i] : i) * hidden;
+    const Tin* src = x + (size_t)(rows ? rows[i] : i) * x_stride;
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float v = to_f32(src[c]);
@@ -339,9 +340,10 @@ static int allow_row(K kernel, size_t bytes) {
 
 SIB_EXPORT int sib_rms_norm(const void* x, int in_dtype, const int* rows, const float* gain,
                             float eps, void* out, int out_dtype, int n_rows, int hidden,
-                            void* stream) {
+                            long long x_stride, void* stream) {
     if (n_rows == 0) return 0;
-    SIB_REQUIRE(n_rows > 0 && hidden > 0, "rms_norm: rows=%d hidden=%d", n_rows, hidden);
+    SIB_REQUIRE(n_rows > 0 && hidden > 0 && x_stride >= hidden, "rms_norm: rows=%d hidden=%d stride=%lld",
+                n_rows, hidden, x_stride);
     const size_t smem = (size_t)hidden * sizeof(float);
     SIB_REQUIRE(smem <= (size_t)kMaxRowBytes,
                 "rms_norm: hidden=%d needs %zu bytes of shared memory; at most %d are supported",
@@ -353,7 +355,7 @@ SIB_EXPORT int sib_rms_norm(const void* x, int in_dtype, const int* rows, const 
         int rc = allow_row(rms_norm_kernel<TIN, TOUT>, smem);                          \
         if (rc) return rc;                                                             \
         sib_launch_chained(rms_norm_kernel<TIN, TOUT>, dim3(n_rows), dim3(threads), smem, s, \
-                           (const TIN*)x, rows, gain, (TOUT*)out, hidden, eps);        \
+                           (const TIN*)x, rows, gain, (TOUT*)out, hidden, eps, x_stride); \
     } while (0)
     if (in_dtype == SIB_F32 && out_dtype == SIB_F32) LAUNCH(float, float);
     else if (in_dtype == SIB_F32 && out_dtype == SIB_BF16) LAUNCH(float, __nv_bfloat16);
@@ -421,8 +423,8 @@ SIB_EXPORT int sib_add_rms_norm(const void* a, int dtype, const float* post_gain
 // Dynamic Tanh: a norm without statistics, element by element
 //     dyt(x) = tanh(alpha x) w + b          (alpha one number, w and b one per column)
 // alone (with a row gather) and fused with the residual add around it, as the RMS norm is:
-//     h[r, :] += post ? dyt_post(a[r, :]) : a[r, :]
-//     out[r, :] = pre ? dyt_pre(h[r, :]) : h[r, :]             (only if out)
+//     h[r, :] += scale * (post ? dyt_post(a[r, :]) : a[r, :])      (scale: the layer's factor
+//     out[r, :] = pre ? dyt_pre(h[r, :]) : h[r, :]   (only if out)  on what it adds; 1 as a rule)
 // Everything is 32-bit; alpha is read from the device (it is a stored tensor).
 // Plain counterpart: tests/plain_vavupel.py dynamic_tanh().
 // ---------------------------------------------------------------------------
@@ -445,7 +447,7 @@ __global__ void add_dyt_norm_kernel(const T* __restrict__ a, const float* __rest
                                     const float* __restrict__ post_b, const float* __restrict__ post_alpha,
                                     float* __restrict__ h, const float* __restrict__ pre_w,
                                     const float* __restrict__ pre_b, const float* __restrict__ pre_alpha,
-                                    T* __restrict__ out, int hidden, size_t total) {
+                                    T* __restrict__ out, int hidden, size_t total, float scale) {
     pdl_trigger();
     pdl_wait();
     const float pa = post_w ? *post_alpha : 0.f, qa = pre_w ? *pre_alpha : 0.f;
@@ -454,7 +456,7 @@ __global__ void add_dyt_norm_kernel(const T* __restrict__ a, const float* __rest
         const int c = (int)(idx % hidden);
         float y = to_f32(a[idx]);
         if (post_w) y = tanhf(pa * y) * post_w[c] + post_b[c];
-        const float s = h[idx] + y;
+        const float s = h[idx] + scale * y;
         h[idx] = s;
         if (out) out[idx] = from_f32<T>(pre_w ? tanhf(qa * s) * pre_w[c] + pre_b[c] : s);
     }
@@ -482,7 +484,7 @@ SIB_EXPORT int sib_dyt_norm(const void* x, int in_dtype, const int* rows, const 
 SIB_EXPORT int sib_add_dyt_norm(const void* a, int dtype, const float* post_w, const float* post_b,
                                 const float* post_alpha, float* h, const float* pre_w,
                                 const float* pre_b, const float* pre_alpha, void* out, int n_rows,
-                                int hidden, void* stream) {
+                                int hidden, float scale, void* stream) {
     if (n_rows == 0) return 0;
     SIB_REQUIRE(n_rows > 0 && hidden > 0, "add_dyt_norm: rows=%d hidden=%d", n_rows, hidden);
     SIB_REQUIRE((post_w == nullptr || (post_b && post_alpha)) && (pre_w == nullptr || (pre_b && pre_alpha && out)),
@@ -493,7 +495,7 @@ SIB_EXPORT int sib_add_dyt_norm(const void* a, int dtype, const float* post_w, c
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(add_dyt_norm_kernel<T>, dim3(blocks), dim3(256), 0,
                                                  (cudaStream_t)stream, (const T*)a, post_w, post_b,
                                                  post_alpha, h, pre_w, pre_b, pre_alpha, (T*)out,
-                                                 hidden, total));
+                                                 hidden, total, scale));
     return sib_check_launch("add_dyt_norm");
 }
 

@@ -554,7 +554,9 @@ SIB_EXPORT int sib_memory_scan(const void* proj, long long stride, int dtype, lo
 // ---------------------------------------------------------------------------
 // Retention, step 1: per row and head, q and k rotated by the row's position on their first
 // `rot` dimensions in half-split pairs (i, i + rot/2; angle pos * inv_freq[i], taken in
-// 32-bit), k then times k_scale; v as it is.  All three leave as 32-bit rows.
+// 32-bit), k then times k_scale; v as it is.  All three leave as 32-bit rows.  `act` 1: q, k
+// and v pass SiLU first, value by value in 32-bit (linear attention whose inputs are
+// activated projections and nothing else).
 // One warp per (row, unit): the q heads, the k heads, the v heads.
 // ---------------------------------------------------------------------------
 struct RetentionPrepareArgs {
@@ -567,6 +569,7 @@ struct RetentionPrepareArgs {
     long long stride;
     int rows, H, kd, vd, rot;
     float k_scale;
+    int act;                 // 0: none, 1: SiLU on q, k and v
 };
 
 template <typename T>
@@ -582,7 +585,10 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(RetentionPrepare
         const int h = unit - 2 * p.H;
         const T* src = row + (size_t)2 * p.H * p.kd + (size_t)h * p.vd;
         float* dst = p.vc + ((size_t)r * p.H + h) * p.vd;
-        for (int d = lane; d < p.vd; d += 32) dst[d] = to_f32(src[d]);
+        for (int d = lane; d < p.vd; d += 32) {
+            const float x = to_f32(src[d]);
+            dst[d] = p.act ? silu_f(x) : x;
+        }
         return;
     }
     const bool is_q = unit < p.H;
@@ -594,11 +600,14 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(RetentionPrepare
     const float post = is_q ? 1.0f : p.k_scale;
     for (int d = lane; d < p.kd; d += 32) {
         float x = to_f32(src[d]);
+        if (p.act) x = silu_f(x);
         if (d < 2 * half) {
             const int i = d < half ? d : d - half;
             const float ang = pos * p.inv_freq[i];
             const float c = cosf(ang), s = sinf(ang);
-            x = d < half ? x * c - to_f32(src[d + half]) * s : x * c + to_f32(src[d - half]) * s;
+            float other = to_f32(src[d < half ? d + half : d - half]);
+            if (p.act) other = silu_f(other);
+            x = d < half ? x * c - other * s : x * c + other * s;
         }
         dst[d] = x * post;
     }
@@ -607,14 +616,14 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(RetentionPrepare
 SIB_EXPORT int sib_retention_prepare(const void* proj, long long stride, int dtype,
                                      const float* inv_freq, int rot, const int* row_pos, float* qn,
                                      float* kn, float* vc, int rows, int H, int kd, int vd,
-                                     float k_scale, void* stream) {
+                                     float k_scale, int act, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && H > 0 && kd > 0 && vd > 0 && row_pos, "retention_prepare: rows=%d heads=%d widths %d, %d",
                 rows, H, kd, vd);
     SIB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= kd && (rot == 0 || inv_freq != nullptr),
                 "retention_prepare: %d rotated dimensions of %d", rot, kd);
     SIB_REQUIRE((3 * H + 3) / 4 < 65536, "retention_prepare: too many heads (%d)", H);
-    RetentionPrepareArgs p{proj, rot ? inv_freq : nullptr, row_pos, qn, kn, vc, stride, rows, H, kd, vd, rot, k_scale};
+    RetentionPrepareArgs p{proj, rot ? inv_freq : nullptr, row_pos, qn, kn, vc, stride, rows, H, kd, vd, rot, k_scale, act};
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(retention_prepare_kernel<T>, dim3(rows, (3 * H + 3) / 4),
                                                  dim3(128), 0, (cudaStream_t)stream, p));
     return sib_check_launch("retention_prepare");

@@ -15,6 +15,13 @@
 //   routed_combine   many rows (experts run as products over sorted rows): the same sum
 //                    from the pairs' outputs, found through the sort's inverse.
 //
+// Two things are parameters of every entry.  `score`: what a chosen expert's weight is,
+// SCORE_SOFTMAX_TOP (the softmax over the chosen logits alone) or SCORE_SIGMOID (the sigmoid of
+// the expert's own logit, not normalized).  `form`: what an expert computes, FORM_CLIPPED_GATED
+// (above; matrices [2 ff, width]) or FORM_PLAIN_GELU, down(gelu(w * up x)) with the exact gelu,
+// matrices [ff, width], where the pair's weight w multiplies what ENTERS the expert (it has no
+// bias, so w * (up x) = up (w x)) and the pairs' outputs are summed as they are.
+//
 // Plain counterpart: tests/plain_gegorax.py routed_ff(), expert().
 #include "common.cuh"
 
@@ -26,12 +33,15 @@ __device__ __forceinline__ float expert_act(float g, float u, float limit, float
     u = fminf(fmaxf(u, -limit), limit);
     return g * sigmoid_r(alpha * g) * (u + 1.0f);
 }
+__device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+constexpr int SCORE_SOFTMAX_TOP = 0, SCORE_SIGMOID = 1;
+constexpr int FORM_CLIPPED_GATED = 0, FORM_PLAIN_GELU = 1;
 
-// One warp: the `top` largest of z[e] + bias[e] in order (ties: the lower index) and the softmax
-// over them alone.
+// One warp: the `top` largest of z[e] + bias[e] in order (ties: the lower index) and their
+// weights: the softmax over them alone, or each one's own sigmoid.
 __device__ __forceinline__ void choose_top(const float* z, const float* __restrict__ bias,
                                            int* __restrict__ ids, float* __restrict__ weights,
-                                           int experts, int top, int lane) {
+                                           int experts, int top, int lane, int score) {
     float first = 0.f, sum = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -49,7 +59,8 @@ __device__ __forceinline__ void choose_top(const float* z, const float* __restri
             if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
         }
         if (k == 0) first = best;
-        const float w = expf(best - first);      // the first chosen logit is the largest
+        // (the first chosen logit is the largest)
+        const float w = score == SCORE_SIGMOID ? sigmoid_r(best) : expf(best - first);
         sum += w;
         if (lane == 0) {
             ids[k] = at;
@@ -57,20 +68,21 @@ __device__ __forceinline__ void choose_top(const float* z, const float* __restri
         }
         __syncwarp();
     }
-    if (lane < top) weights[lane] /= sum;
+    if (score == SCORE_SOFTMAX_TOP && lane < top) weights[lane] /= sum;
 }
 
 // One warp per row.
 __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                   int* __restrict__ ids, float* __restrict__ weights, int rows, int experts, int top) {
+                   int* __restrict__ ids, float* __restrict__ weights, int rows, int experts, int top,
+                   int score) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (r >= rows) return;
     choose_top(logits + (size_t)r * experts, bias, ids + (size_t)r * top, weights + (size_t)r * top,
-               experts, top, lane);
+               experts, top, lane, score);
 }
 
 // Few rows: the router's product and the choice in one launch.  One block per row: the row in
@@ -80,7 +92,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 router_rows_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
                    const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
-                   int width, int experts, int top) {
+                   int width, int experts, int top, int score) {
     extern __shared__ __align__(16) float sh[];      // [width] the row, [experts] its logits
     float* xs = sh;
     float* z = sh + ((width + 3) & ~3);
@@ -107,21 +119,26 @@ router_rows_kernel(const T* __restrict__ x, long long x_stride, const float* __r
     }
     __syncthreads();
     if (warp == 0)
-        choose_top(z, bias, ids + (size_t)r * top, weights + (size_t)r * top, experts, top, lane);
+        choose_top(z, bias, ids + (size_t)r * top, weights + (size_t)r * top, experts, top, lane, score);
 }
 
 template <typename T>
 __global__ void expert_activate_kernel(const T* __restrict__ gu, long long stride, T* __restrict__ y,
                                        const float* __restrict__ row_weight, int ff, float limit,
-                                       float alpha, size_t total) {
+                                       float alpha, size_t total, int form) {
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / ff;
         const int j = (int)(i - r * ff);
-        float v = expert_act(to_f32(gu[r * stride + j]), to_f32(gu[r * stride + ff + j]), limit, alpha);
-        if (row_weight) v *= row_weight[r];
+        float v;
+        if (form == FORM_PLAIN_GELU) {       // rows [up (ff)]; the row's weight on what enters the gelu
+            v = gelu_erf(to_f32(gu[r * stride + j]) * (row_weight ? row_weight[r] : 1.0f));
+        } else {
+            v = expert_act(to_f32(gu[r * stride + j]), to_f32(gu[r * stride + ff + j]), limit, alpha);
+            if (row_weight) v *= row_weight[r];
+        }
         y[i] = from_f32<T>(v);
     }
 }
@@ -185,12 +202,13 @@ __device__ __forceinline__ bool reads_wide(const T* base, int width) {
 }
 
 // grid (tiles of middle columns, pairs); a block: 4 warps, one pair's x row; a warp takes two
-// middle columns at a time: four matrix rows (two gates, two ups) in flight.
-template <typename T>
+// middle columns at a time: four matrix rows (two gates, two ups) in flight.  PLAIN (experts
+// without a gate): four middle columns at a time, the pair's weight on what enters the gelu.
+template <typename T, bool PLAIN>
 __global__ void __launch_bounds__(128)
 routed_rows_gate_up_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ w_gu,
-                           const int* __restrict__ ids, T* __restrict__ mid, int width, int ff,
-                           int top, float limit, float alpha) {
+                           const int* __restrict__ ids, const float* __restrict__ pair_weight,
+                           T* __restrict__ mid, int width, int ff, int top, float limit, float alpha) {
     extern __shared__ __align__(16) float xs[];
     pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -200,9 +218,25 @@ routed_rows_gate_up_kernel(const T* __restrict__ x, long long x_stride, const T*
     const T* row = x + (size_t)(pair / top) * x_stride;
     for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(row[c]);
     __syncthreads();
-    const T* w = w_gu + (size_t)e * 2 * ff * width;
+    const T* w = w_gu + (size_t)e * (PLAIN ? 1 : 2) * ff * width;
     const bool wide = reads_wide(w_gu, width);
     const float* const xv[4] = {xs, xs, xs, xs};
+    if constexpr (PLAIN) {
+        const float pw = pair_weight ? pair_weight[pair] : 1.0f;
+        for (int j = (blockIdx.x * 4 + warp) * 4; j < ff; j += gridDim.x * 16) {
+            const T* const rows[4] = {w + (size_t)j * width, w + (size_t)min(j + 1, ff - 1) * width,
+                                      w + (size_t)min(j + 2, ff - 1) * width,
+                                      w + (size_t)min(j + 3, ff - 1) * width};
+            float d[4];
+            rows_dot<T, 4>(rows, xv, width, lane, wide, d);
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (j + i < ff) mid[(size_t)pair * ff + j + i] = from_f32<T>(gelu_erf(d[i] * pw));
+            }
+        }
+        return;
+    }
     for (int j = (blockIdx.x * 4 + warp) * 2; j < ff; j += gridDim.x * 8) {
         const int j1 = min(j + 1, ff - 1);
         const T* const rows[4] = {w + (size_t)j * width, w + (size_t)(ff + j) * width,
@@ -246,7 +280,7 @@ routed_rows_down_kernel(const T* __restrict__ mid, const T* __restrict__ w_down,
             rows_dot<T, 4>(rows, mv, ff, lane, wide, d);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                if (k0 + i < top) acc += weights[(size_t)r * top + k0 + i] * d[i];
+                if (k0 + i < top) acc += (weights ? weights[(size_t)r * top + k0 + i] : 1.0f) * d[i];
         }
         if (lane == 0) out[(size_t)r * width + n] = from_f32<T>(acc);
     }
@@ -267,11 +301,12 @@ __device__ __forceinline__ int pairs_of_expert(const int* __restrict__ ids, int 
     return *count;
 }
 
-template <typename T>
+template <typename T, bool PLAIN>
 __global__ void __launch_bounds__(128)
 routed_expert_gate_up_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ w_gu,
-                             const int* __restrict__ ids, T* __restrict__ mid, int width, int ff,
-                             int top, int pairs, float limit, float alpha) {
+                             const int* __restrict__ ids, const float* __restrict__ pair_weight,
+                             T* __restrict__ mid, int width, int ff, int top, int pairs, float limit,
+                             float alpha) {
     extern __shared__ __align__(16) float sh[];      // [width] a row, then the list of pairs
     __shared__ int count;
     float* xs = sh;
@@ -282,9 +317,9 @@ routed_expert_gate_up_kernel(const T* __restrict__ x, long long x_stride, const 
     pdl_wait();
     const int n = pairs_of_expert(ids, pairs, e, list, &count);
     if (n == 0) return;
-    const T* w = w_gu + (size_t)e * 2 * ff * width;
+    const T* w = w_gu + (size_t)e * (PLAIN ? 1 : 2) * ff * width;
     const bool wide = reads_wide(w_gu, width);
-    const int j = (blockIdx.x * 4 + warp) * 2, j1 = min(j + 1, ff - 1);
+    const int j = (blockIdx.x * 4 + warp) * (PLAIN ? 4 : 2), j1 = min(j + 1, ff - 1);
     const float* const xv[4] = {xs, xs, xs, xs};
     for (int q = 0; q < n; ++q) {
         const int pair = list[q];
@@ -292,7 +327,21 @@ routed_expert_gate_up_kernel(const T* __restrict__ x, long long x_stride, const 
         __syncthreads();
         for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(row[c]);
         __syncthreads();
-        if (j < ff) {
+        if constexpr (PLAIN) {
+            if (j < ff) {
+                const T* const rows[4] = {w + (size_t)j * width, w + (size_t)j1 * width,
+                                          w + (size_t)min(j + 2, ff - 1) * width,
+                                          w + (size_t)min(j + 3, ff - 1) * width};
+                float d[4];
+                rows_dot<T, 4, true>(rows, xv, width, lane, wide, d);
+                const float pw = pair_weight ? pair_weight[pair] : 1.0f;
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (j + i < ff) mid[(size_t)pair * ff + j + i] = from_f32<T>(gelu_erf(d[i] * pw));
+                }
+            }
+        } else if (j < ff) {
             const T* const rows[4] = {w + (size_t)j * width, w + (size_t)(ff + j) * width,
                                       w + (size_t)j1 * width, w + (size_t)(ff + j1) * width};
             float d[4];
@@ -355,7 +404,7 @@ __global__ void routed_combine_kernel(const T* __restrict__ ys, const int* __res
         const int n = (int)(i - r * width);
         float acc = base ? to_f32(base[i]) : 0.f;
         for (int k = 0; k < top; ++k)
-            acc += weights[r * top + k] * to_f32(ys[(size_t)where[r * top + k] * width + n]);
+            acc += (weights ? weights[r * top + k] : 1.0f) * to_f32(ys[(size_t)where[r * top + k] * width + n]);
         out[i] = from_f32<T>(acc);
     }
 }
@@ -368,19 +417,19 @@ int grid_for(size_t total) {
 }  // namespace
 
 SIB_EXPORT int sib_router_topk(const float* logits, const float* bias, int* ids, float* weights,
-                               int rows, int experts, int top, void* stream) {
+                               int rows, int experts, int top, int score, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && experts > 0 && top > 0 && top <= experts && top <= 32,
                 "router_topk: rows=%d experts=%d top=%d (at most 32 and the number of experts)",
                 rows, experts, top);
     sib_launch_chained(router_topk_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
-                       logits, bias, ids, weights, rows, experts, top);
+                       logits, bias, ids, weights, rows, experts, top, score);
     return sib_check_launch("router_topk");
 }
 
 SIB_EXPORT int sib_router_rows(const void* x, long long x_stride, int dtype, const float* w,
                                const float* bias, int* ids, float* weights, int rows, int width,
-                               int experts, int top, void* stream) {
+                               int experts, int top, int score, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && width > 0 && experts > 0 && top > 0 && top <= experts && top <= 32,
                 "router_rows: rows=%d width=%d experts=%d top=%d", rows, width, experts, top);
@@ -389,26 +438,27 @@ SIB_EXPORT int sib_router_rows(const void* x, long long x_stride, int dtype, con
                 width, experts);
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(router_rows_kernel<T>, dim3(rows), dim3(256), shared,
                                                  (cudaStream_t)stream, (const T*)x, x_stride, w, bias,
-                                                 ids, weights, width, experts, top));
+                                                 ids, weights, width, experts, top, score));
     return sib_check_launch("router_rows");
 }
 
 SIB_EXPORT int sib_expert_activate(const void* gu, long long stride, void* y, const float* row_weight,
-                                   int dtype, int rows, int ff, float limit, float alpha,
+                                   int dtype, int rows, int ff, float limit, float alpha, int form,
                                    void* stream) {
     if (rows == 0) return 0;
-    SIB_REQUIRE(rows > 0 && ff > 0 && stride >= 2 * ff, "expert_activate: rows=%d ff=%d", rows, ff);
+    SIB_REQUIRE(rows > 0 && ff > 0 && stride >= (form == FORM_PLAIN_GELU ? 1 : 2) * ff,
+                "expert_activate: rows=%d ff=%d", rows, ff);
     const size_t total = (size_t)rows * ff;
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(expert_activate_kernel<T>, dim3(grid_for(total)),
                                                  dim3(256), 0, (cudaStream_t)stream, (const T*)gu,
-                                                 stride, (T*)y, row_weight, ff, limit, alpha, total));
+                                                 stride, (T*)y, row_weight, ff, limit, alpha, total, form));
     return sib_check_launch("expert_activate");
 }
 
 SIB_EXPORT int sib_routed_rows(const void* x, long long x_stride, const void* w_gu, const void* w_down,
                                const int* ids, const float* weights, const void* base, void* mid,
                                void* out, int dtype, int rows, int width, int ff, int top,
-                               float limit, float alpha, void* stream) {
+                               float limit, float alpha, int form, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && rows * (long long)top < 65536 && width > 0 && ff > 0 && top > 0,
                 "routed_rows: rows=%d top=%d width=%d ff=%d", rows, top, width, ff);
@@ -416,17 +466,28 @@ SIB_EXPORT int sib_routed_rows(const void* x, long long x_stride, const void* w_
                 "routed_rows: rows of %d and %d x %d do not fit shared memory", width, top, ff);
     cudaStream_t s = (cudaStream_t)stream;
     const int pairs = rows * top;
-    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_rows_gate_up_kernel<T>,
-                                                 dim3(min((ff + 7) / 8, 64), pairs), dim3(128),
-                                                 (size_t)width * 4, s, (const T*)x, x_stride,
-                                                 (const T*)w_gu, ids, (T*)mid, width, ff, top, limit,
-                                                 alpha));
+    const bool plain = form == FORM_PLAIN_GELU;
+    // (experts without a gate weigh what enters them: the pairs' outputs are summed as they are)
+    const float* out_weights = plain ? nullptr : weights;
+    if (plain) {
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_rows_gate_up_kernel<T, true>,
+                                                     dim3(min((ff + 15) / 16, 64), pairs), dim3(128),
+                                                     (size_t)width * 4, s, (const T*)x, x_stride,
+                                                     (const T*)w_gu, ids, weights, (T*)mid, width, ff,
+                                                     top, limit, alpha));
+    } else {
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_rows_gate_up_kernel<T, false>,
+                                                     dim3(min((ff + 7) / 8, 64), pairs), dim3(128),
+                                                     (size_t)width * 4, s, (const T*)x, x_stride,
+                                                     (const T*)w_gu, ids, weights, (T*)mid, width, ff,
+                                                     top, limit, alpha));
+    }
     int rc = sib_check_launch("routed_rows_gate_up");
     if (rc) return rc;
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_rows_down_kernel<T>,
                                                  dim3(min((width + 3) / 4, 64), rows), dim3(128),
                                                  (size_t)top * ff * 4, s, (const T*)mid,
-                                                 (const T*)w_down, ids, weights, (const T*)base,
+                                                 (const T*)w_down, ids, out_weights, (const T*)base,
                                                  (T*)out, width, ff, top));
     return sib_check_launch("routed_rows_down");
 }
@@ -437,18 +498,28 @@ SIB_EXPORT int sib_routed_by_expert(const void* x, long long x_stride, const voi
                                     const void* w_down, const int* ids, const float* weights,
                                     const void* base, void* mid, void* ys, const int* order, void* out,
                                     int dtype, int rows, int width, int ff, int top, int experts,
-                                    float limit, float alpha, void* stream) {
+                                    float limit, float alpha, int form, void* stream) {
     if (rows == 0) return 0;
     const long long pairs = (long long)rows * top;
     SIB_REQUIRE(rows > 0 && width > 0 && ff > 0 && top > 0 && experts > 0 && experts < 65536 &&
                     ((size_t)max(width, ff) + 4 + pairs) * 4 <= 48 * 1024,
                 "routed_by_expert: rows=%d top=%d width=%d ff=%d experts=%d", rows, top, width, ff, experts);
     cudaStream_t s = (cudaStream_t)stream;
-    SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_expert_gate_up_kernel<T>,
-                                                 dim3((ff + 7) / 8, experts), dim3(128),
-                                                 ((size_t)((width + 3) & ~3) + pairs) * 4, s,
-                                                 (const T*)x, x_stride, (const T*)w_gu, ids, (T*)mid,
-                                                 width, ff, top, (int)pairs, limit, alpha));
+    const bool plain = form == FORM_PLAIN_GELU;
+    const float* out_weights = plain ? nullptr : weights;
+    if (plain) {
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_expert_gate_up_kernel<T, true>,
+                                                     dim3((ff + 15) / 16, experts), dim3(128),
+                                                     ((size_t)((width + 3) & ~3) + pairs) * 4, s,
+                                                     (const T*)x, x_stride, (const T*)w_gu, ids, weights,
+                                                     (T*)mid, width, ff, top, (int)pairs, limit, alpha));
+    } else {
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_expert_gate_up_kernel<T, false>,
+                                                     dim3((ff + 7) / 8, experts), dim3(128),
+                                                     ((size_t)((width + 3) & ~3) + pairs) * 4, s,
+                                                     (const T*)x, x_stride, (const T*)w_gu, ids, weights,
+                                                     (T*)mid, width, ff, top, (int)pairs, limit, alpha));
+    }
     int rc = sib_check_launch("routed_expert_gate_up");
     if (rc) return rc;
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_expert_down_kernel<T>,
@@ -460,7 +531,7 @@ SIB_EXPORT int sib_routed_by_expert(const void* x, long long x_stride, const voi
     if (rc) return rc;
     const size_t total = (size_t)rows * width;
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_combine_kernel<T>, dim3(grid_for(total)),
-                                                 dim3(256), 0, s, (const T*)ys, order, weights,
+                                                 dim3(256), 0, s, (const T*)ys, order, out_weights,
                                                  (const T*)base, (T*)out, width, top, total));
     return sib_check_launch("routed_combine");
 }

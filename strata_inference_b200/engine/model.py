@@ -121,7 +121,7 @@ class DecoderModel:
             norms = {site: parts.part_class("norm", n.kind)(
                 n.params, H, _sub(weights, layer.prefix + layer.names[site]), rt)
                 for site, n in layer.norms.items()}
-            extra = {}
+            extra = dict(layer.block_params)
             if layer.tail is not None:
                 extra["tail"] = parts.part_class("tail", layer.tail.kind)(
                     layer.tail.params, H, _sub(weights, layer.prefix + layer.names["tail"]), rt)

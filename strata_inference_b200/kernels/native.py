@@ -27,6 +27,8 @@ ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
 ACT_RELU_SQUARED = 2                    # of the feed-forward without a gate (activate)
 ACT_TANH = 3                            # tanh, value by value (activate)
 GATE_SILU, GATE_SIGMOID = 0, 1          # of head_norm_gate
+SCORE_SOFTMAX_TOP, SCORE_SIGMOID = 0, 1     # of the routers: what a chosen expert's weight is
+FORM_CLIPPED_GATED, FORM_PLAIN_GELU = 0, 1  # of the routed experts: what an expert computes
 
 _lib = None
 
@@ -236,11 +238,14 @@ def _timed(work: Callable):
     return deco
 
 
-def _attention_cache_work(kind, row_pos, k_pool, n_heads, head_dim, window, rows, value_dim=None):
+def _attention_cache_work(kind, row_pos, k_pool, n_heads, head_dim, window, rows, value_dim=None,
+                          chunk=0):
     """Keys and values a row at ``row_pos`` reads from the cache (reads the positions back:
     only done under a profile)."""
     seen = row_pos.to(torch.int64) + 1
-    if window > 0:
+    if chunk > 0:
+        seen = row_pos.to(torch.int64) % chunk + 1
+    elif window > 0:
         seen = seen.clamp(max=window)
     keys = int(seen.sum().item())
     n_kv = k_pool.shape[1]
@@ -332,12 +337,13 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     "rms_norm", out.shape[0] * x.shape[1] * x.element_size() + _nbytes(out), 0))
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = rms(x[rows[i] if rows else i]) * gain; statistics in 32-bit."""
+    """out[i] = rms(x[rows[i] if rows else i]) * gain; statistics in 32-bit.  ``x`` may be a
+    view of the leading columns of a wider buffer."""
     _want(gain, torch.float32, "gain")
-    _want(x, x.dtype, "x")
+    _want(x, x.dtype, "x", contiguous=False)
     _want(out, out.dtype, "out")
     n, hidden = out.shape
-    if x.shape[1] != hidden or gain.numel() != hidden:
+    if x.shape[1] != hidden or gain.numel() != hidden or x.stride(1) != 1:
         raise KernelError("rms_norm: shapes do not fit")
     if rows is not None:
         _want(rows, torch.int32, "rows")
@@ -346,7 +352,8 @@ def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
     elif x.shape[0] != n:
         raise KernelError("rms_norm: x and out differ in rows")
     _check(library().sib_rms_norm(_ptr(x), _code(x.dtype), _ptr(rows), _ptr(gain), c_float(eps),
-                                  _ptr(out), _code(out.dtype), c_int(n), c_int(hidden), _stream()))
+                                  _ptr(out), _code(out.dtype), c_int(n), c_int(hidden),
+                                  c_longlong(x.stride(0)), _stream()))
     return out
 
 
@@ -400,11 +407,12 @@ def dyt_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Ten
     return out
 
 
-@_timed(lambda a, post, h, pre, out: ("add_dyt_norm", _nbytes(a, out) + 2 * _nbytes(h), 0))
-def add_dyt_norm(a: torch.Tensor, post, h: torch.Tensor, pre, out: Optional[torch.Tensor]) -> None:
-    """h += dyt_post(a) (or a when ``post`` is None); out = dyt_pre(h) (or h as activations
-    when ``pre`` is None and out is given).  ``post`` and ``pre``: (w, b, alpha) of a Dynamic
-    Tanh, 32-bit on the device."""
+@_timed(lambda a, post, h, pre, out, scale=1.0: ("add_dyt_norm", _nbytes(a, out) + 2 * _nbytes(h), 0))
+def add_dyt_norm(a: torch.Tensor, post, h: torch.Tensor, pre, out: Optional[torch.Tensor],
+                 scale: float = 1.0) -> None:
+    """h += scale * dyt_post(a) (or scale * a when ``post`` is None); out = dyt_pre(h) (or h as
+    activations when ``pre`` is None and out is given).  ``post`` and ``pre``: (w, b, alpha) of
+    a Dynamic Tanh, 32-bit on the device."""
     _want(h, torch.float32, "h")
     _want(a, a.dtype, "a")
     rows, hidden = h.shape
@@ -425,7 +433,7 @@ def add_dyt_norm(a: torch.Tensor, post, h: torch.Tensor, pre, out: Optional[torc
     qw, qb, qa = pre if pre is not None else (None, None, None)
     _check(library().sib_add_dyt_norm(_ptr(a), _code(a.dtype), _ptr(pw), _ptr(pb), _ptr(pa), _ptr(h),
                                       _ptr(qw), _ptr(qb), _ptr(qa), _ptr(out), c_int(rows),
-                                      c_int(hidden), _stream()))
+                                      c_int(hidden), c_float(scale), _stream()))
 
 
 @_timed(lambda ctx, table, bigram, last_token, out, *a: ("bigram_embed", 3 * _nbytes(out), 0))
@@ -505,11 +513,12 @@ def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
     return y
 
 
-@_timed(lambda logits, bias, ids, weights: ("router_topk", _nbytes(logits, ids, weights), 0))
+@_timed(lambda logits, bias, ids, weights, *a: ("router_topk", _nbytes(logits, ids, weights), 0))
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
-                weights: torch.Tensor) -> None:
+                weights: torch.Tensor, score: int = SCORE_SOFTMAX_TOP) -> None:
     """Per row of the 32-bit ``logits`` (+ ``bias``): the ``top`` = ids.shape[1] largest (ties: the
-    lower index) into ``ids`` (int32) and the softmax over those alone into ``weights``."""
+    lower index) into ``ids`` (int32) and into ``weights`` the softmax over those alone
+    (SCORE_SOFTMAX_TOP) or each one's own sigmoid (SCORE_SIGMOID)."""
     rows, experts = logits.shape
     top = ids.shape[1]
     _want(logits, torch.float32, "logits")
@@ -520,12 +529,12 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.T
     if ids.shape[0] != rows:
         raise KernelError("router_topk: one row of choices per row of logits")
     _check(library().sib_router_topk(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), c_int(rows),
-                                     c_int(experts), c_int(top), _stream()))
+                                     c_int(experts), c_int(top), c_int(score), _stream()))
 
 
-@_timed(lambda x, w, bias, ids, weights: ("router_rows", _nbytes(x, w), 2.0 * x.shape[0] * w.numel()))
+@_timed(lambda x, w, bias, ids, weights, *a: ("router_rows", _nbytes(x, w), 2.0 * x.shape[0] * w.numel()))
 def router_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
-                weights: torch.Tensor) -> None:
+                weights: torch.Tensor, score: int = SCORE_SOFTMAX_TOP) -> None:
     """Few rows: z = w x (+ ``bias``) with the 32-bit matrix ``w`` ``[experts, width]`` and the
     choice of :func:`router_topk`, in one launch; sums are 32-bit."""
     rows, width = x.shape
@@ -540,39 +549,43 @@ def router_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         raise KernelError("router_rows: shapes do not fit")
     _check(library().sib_router_rows(_ptr(x), c_longlong(x.stride(0)), _code(x.dtype), _ptr(w), _ptr(bias),
                                      _ptr(ids), _ptr(weights), c_int(rows), c_int(width),
-                                     c_int(experts), c_int(top), _stream()))
+                                     c_int(experts), c_int(top), c_int(score), _stream()))
 
 
-@_timed(lambda gu, y, row_weight, limit, alpha: ("expert_activate", _nbytes(gu, y), 0))
+@_timed(lambda gu, y, row_weight, limit, alpha, *a: ("expert_activate", _nbytes(gu, y), 0))
 def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torch.Tensor],
-                    limit: float, alpha: float) -> torch.Tensor:
-    """y = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit),
-    from rows ``[gate (ff) | up (ff)]``; with ``row_weight`` every row times its 32-bit weight."""
+                    limit: float, alpha: float, form: int = FORM_CLIPPED_GATED) -> torch.Tensor:
+    """FORM_CLIPPED_GATED: y = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up,
+    -limit, limit), from rows ``[gate (ff) | up (ff)]``; with ``row_weight`` every row times its
+    32-bit weight.  FORM_PLAIN_GELU: y = gelu(row_weight * up), the exact gelu, from rows ``[up
+    (ff)]``."""
     rows, ff = y.shape
     _want(gu, y.dtype, "gu", contiguous=False)
     _want(y, y.dtype, "y")
-    if gu.shape[0] != rows or gu.shape[1] != 2 * ff or gu.stride(1) != 1:
-        raise KernelError("expert_activate: rows of gate | up")
+    if gu.shape[0] != rows or gu.shape[1] != (1 if form == FORM_PLAIN_GELU else 2) * ff or gu.stride(1) != 1:
+        raise KernelError("expert_activate: rows of gate | up (or of up alone)")
     if row_weight is not None:
         _f32(row_weight, rows, "row_weight")
     _check(library().sib_expert_activate(_ptr(gu), c_longlong(gu.stride(0)), _ptr(y), _ptr(row_weight),
                                          _code(y.dtype), c_int(rows), c_int(ff), c_float(limit),
-                                         c_float(alpha), _stream()))
+                                         c_float(alpha), c_int(form), _stream()))
     return y
 
 
 _PAIR_ORDER: dict = {}
 
 
-@_timed(lambda x, w_gu, w_down, ids, weights, base, out, limit, alpha: (
-    "routed_rows", min(ids.numel(), w_down.shape[0]) * 3 * w_down.shape[1] * w_down.shape[2] * x.element_size(),
-    6.0 * ids.numel() * w_down.shape[1] * w_down.shape[2]))
+@_timed(lambda x, w_gu, w_down, ids, weights, base, out, limit, alpha, form=0: (
+    "routed_rows", min(ids.numel(), w_down.shape[0]) * (2 if form else 3) * w_down.shape[1] * w_down.shape[2]
+    * x.element_size(), (4.0 if form else 6.0) * ids.numel() * w_down.shape[1] * w_down.shape[2]))
 def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                 weights: torch.Tensor, base: Optional[torch.Tensor], out: torch.Tensor,
-                limit: float, alpha: float) -> torch.Tensor:
+                limit: float, alpha: float, form: int = FORM_CLIPPED_GATED) -> torch.Tensor:
     """The chosen experts of every row, each (row, expert) pair streaming its expert's matrices
     (csrc/routed.cu): ``w_gu`` ``[experts, 2 ff, width]`` (gate rows, then up rows), ``w_down``
     ``[experts, width, ff]``; out = base + sum_k weights[r, k] down(act(gate, up)) in 32-bit.
+    FORM_PLAIN_GELU: ``w_gu`` ``[experts, ff, width]`` (up rows alone), out = base + sum_k
+    down(gelu(weights[r, k] * up)).
     With more pairs than half the experts the kernels go expert by expert instead (an expert's
     matrices are read once for all the pairs that chose it)."""
     rows, width = x.shape
@@ -583,7 +596,8 @@ def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: 
         _want(t, x.dtype, nm)
     _want(ids, torch.int32, "ids")
     _f32(weights, rows * top, "weights")
-    if tuple(w_gu.shape) != (experts, 2 * ff, width) or w_down.shape[1] != width or x.stride(1) != 1 \
+    if tuple(w_gu.shape) != (experts, (1 if form == FORM_PLAIN_GELU else 2) * ff, width) \
+            or w_down.shape[1] != width or x.stride(1) != 1 \
             or tuple(out.shape) != (rows, width) or ids.shape[0] != rows:
         raise KernelError("routed_rows: shapes do not fit")
     if base is not None:
@@ -599,26 +613,29 @@ def routed_rows(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: 
         _check(library().sib_routed_by_expert(
             _ptr(x), c_longlong(x.stride(0)), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
             _ptr(base), _ptr(mid), _ptr(ys), _ptr(order), _ptr(out), _code(x.dtype), c_int(rows),
-            c_int(width), c_int(ff), c_int(top), c_int(experts), c_float(limit), c_float(alpha), _stream()))
+            c_int(width), c_int(ff), c_int(top), c_int(experts), c_float(limit), c_float(alpha),
+            c_int(form), _stream()))
         return out
     _check(library().sib_routed_rows(
         _ptr(x), c_longlong(x.stride(0)), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
         _ptr(base), _ptr(mid), _ptr(out), _code(x.dtype), c_int(rows), c_int(width), c_int(ff),
-        c_int(top), c_float(limit), c_float(alpha), _stream()))
+        c_int(top), c_float(limit), c_float(alpha), c_int(form), _stream()))
     return out
 
 
 @_timed(lambda ys, where, weights, base, out: ("routed_combine", _nbytes(ys, out), 0))
-def routed_combine(ys: torch.Tensor, where: torch.Tensor, weights: torch.Tensor,
+def routed_combine(ys: torch.Tensor, where: torch.Tensor, weights: Optional[torch.Tensor],
                    base: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """out[r] = base[r] + sum_k weights[r, k] ys[where[r, k]] in 32-bit: the rows' sums over the
-    outputs of their (row, expert) pairs, which lie sorted by expert."""
+    outputs of their (row, expert) pairs, which lie sorted by expert.  ``weights`` None: the plain
+    sum."""
     rows, width = out.shape
     top = where.shape[1]
     _want(ys, out.dtype, "ys")
     _want(out, out.dtype, "out")
     _want(where, torch.int32, "where")
-    _f32(weights, rows * top, "weights")
+    if weights is not None:
+        _f32(weights, rows * top, "weights")
     if ys.shape[1] != width or where.shape[0] != rows:
         raise KernelError("routed_combine: shapes do not fit")
     if base is not None:
@@ -767,10 +784,11 @@ def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor
                    c_gain: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot: int, ctx,
                    k_pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
                    page_tokens: int, ring_tokens: int, n_heads: int, q_dim: int, rot_dim: int,
-                   rank: int, pad: int) -> None:
+                   rank: int, pad: int, down: Optional[torch.Tensor] = None) -> None:
     """Between the projections and the attention over a shared latent (csrc/head_prepare.cu):
     ``proj`` rows hold the query heads (``q_dim`` + ``rot_dim`` each) and then the down
-    projection (``rank`` + ``rot_dim``); ``q_lat`` ``[heads, rows, rank]`` are the queries
+    projection (``rank`` + ``rot_dim``), unless ``down`` (a view ``[rows, rank + rot_dim]``) gives
+    the latter where the queries come from a product of their own; ``q_lat`` ``[heads, rows, rank]`` are the queries
     already multiplied into the latent's space.  Writes ``q_rows`` ``[rows, heads * pad]``
     (not with ``q_lat`` and ``q_rows`` None), ``k_rows`` ``[rows, pad]`` and the cache cells of
     the rows."""
@@ -785,8 +803,12 @@ def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor
         _want(t, proj.dtype, nm)
         if tuple(t.shape) != shape:
             raise KernelError(f"latent_prepare: {nm} must be {shape}")
-    if proj.stride(1) != 1 or proj.shape[1] < n_heads * (q_dim + rot_dim) + rank + rot_dim:
+    if proj.stride(1) != 1 or proj.shape[1] < n_heads * (q_dim + rot_dim) + (0 if down is not None else rank + rot_dim):
         raise KernelError("latent_prepare: a projected row must hold the query heads and the down projection")
+    if down is not None:
+        _want(down, proj.dtype, "down", contiguous=False)
+        if down.stride(1) != 1 or down.shape[0] != rows or down.shape[1] < rank + rot_dim:
+            raise KernelError("latent_prepare: down must be [rows, rank + rot_dim]")
     _f32(c_gain, rank, "c_gain")
     if rot:
         _f32(inv_freq, rot // 2, "inv_freq")
@@ -801,7 +823,8 @@ def latent_prepare(proj: torch.Tensor, q_lat: torch.Tensor, q_rows: torch.Tensor
         _code(proj.dtype), _ptr(c_gain), c_float(eps), _ptr(inv_freq if rot else None), c_int(rot),
         _ptr(ctx.row_pos), _ptr(ctx.row_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_end), _ptr(k_pool),
         _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens), c_int(rows),
-        c_int(n_heads), c_int(q_dim), c_int(rot_dim), c_int(rank), c_int(pad), _stream()))
+        c_int(n_heads), c_int(q_dim), c_int(rot_dim), c_int(rank), c_int(pad), _ptr(down),
+        c_longlong(down.stride(0) if down is not None else 0), _stream()))
 
 
 @_timed(lambda proj, k_rows, k_heads, v_heads, qkv, *a, **kw: ("latent_expand", _nbytes(k_heads, v_heads, qkv) * 1.3, 0))
@@ -936,9 +959,10 @@ def memory_scan(proj: torch.Tensor, bias_i: torch.Tensor, bias_f: torch.Tensor, 
     + _nbytes(qn, kn, vc), 0))
 def retention_prepare(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot: int, row_pos,
                       qn: torch.Tensor, kn: torch.Tensor, vc: torch.Tensor, n_heads: int,
-                      key_dim: int, value_dim: int, k_scale: float) -> None:
+                      key_dim: int, value_dim: int, k_scale: float, silu: bool = False) -> None:
     """From projected rows ``[q | k | v | ...]``: q and k rotated on their first ``rot``
-    dimensions (half-split pairs), k times ``k_scale``, v as it is; all 32-bit."""
+    dimensions (half-split pairs), k times ``k_scale``, v as it is; all 32-bit.  ``silu``: q, k
+    and v pass SiLU first."""
     rows = proj.shape[0]
     _want(proj, proj.dtype, "proj", contiguous=False)
     if proj.stride(1) != 1 or proj.shape[1] < n_heads * (2 * key_dim + value_dim):
@@ -951,7 +975,7 @@ def retention_prepare(proj: torch.Tensor, inv_freq: Optional[torch.Tensor], rot:
     _check(library().sib_retention_prepare(
         _ptr(proj), c_longlong(proj.stride(0)), _code(proj.dtype), _ptr(inv_freq if rot else None),
         c_int(rot), _ptr(row_pos), _ptr(qn), _ptr(kn), _ptr(vc), c_int(rows), c_int(n_heads),
-        c_int(key_dim), c_int(value_dim), c_float(k_scale), _stream()))
+        c_int(key_dim), c_int(value_dim), c_float(k_scale), c_int(1 if silu else 0), _stream()))
 
 
 @_timed(lambda qn, kn, vc, decay, state, out, ctx, n_heads, key_dim, value_dim: _scan_work(
@@ -1144,10 +1168,10 @@ def attention_rows_scratch_bytes(rows: int, n_heads: int, head_dim: int, splits:
 @_timed(lambda q, q_stride, k_new, v_new, kv_stride, k_pool, v_pool, page_table, page_tokens,
         ring_tokens, row_pos, row_seq, seq_slot, seq_start, seq_row0, out, scratch, n_heads, n_kv,
         head_dim, scale, softcap, window, splits, sink=None, values_in_keys=False, cells=None,
-        cells_only=False: (
+        cells_only=False, chunk=0: (
             ("attention_rows (blocks)", _nbytes(out), 0) if cells_only else
             _attention_cache_work("attention_rows (cache)", row_pos, k_pool, n_heads, head_dim,
-                                  window, out.shape[0]) if k_pool is not None else
+                                  window, out.shape[0], chunk=chunk) if k_pool is not None else
             ("attention_rows (prompt)", 2 * _nbytes(out) * (1 + 2 * n_kv / n_heads),
              2.0 * (row_pos.to(torch.int64) + 1).sum().item() * 2 * n_heads * head_dim)))
 def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor],
@@ -1158,8 +1182,10 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
                    scratch: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                    scale: float, softcap: float, window: int, splits: int,
                    sink: Optional[torch.Tensor] = None, values_in_keys: bool = False,
-                   cells=None, cells_only: bool = False) -> torch.Tensor:
-    """General attention of independent rows (see csrc/attention_rows.cu).  ``sink``: one
+                   cells=None, cells_only: bool = False, chunk: int = 0) -> torch.Tensor:
+    """General attention of independent rows (see csrc/attention_rows.cu).  ``chunk`` > 0
+    (without a window): a row sees the positions of its own chunk of that many, chunks
+    counted from the sequence's first position.  ``sink``: one
     32-bit value per query head whose exponential joins the softmax's denominator.
     ``values_in_keys``: a value is its key's cell (``v_new`` / ``v_pool`` are not read).
     ``cells``: a cache view (``KVView``) with cells of pooled blocks; a row then also sees
@@ -1189,7 +1215,7 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_new: Optional[torch.Tensor]
         _ptr(v_pool), _ptr(page_table), c_int(max_pages), c_int(page_tokens), c_int(ring_tokens),
         _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_row0), _ptr(out),
         _ptr(scratch), _code(out.dtype), c_int(rows), c_int(n_heads), c_int(n_kv), c_int(head_dim),
-        c_float(scale), c_float(softcap), c_int(window), c_int(splits), _ptr(sink),
+        c_float(scale), c_float(softcap), c_int(window), c_int(chunk), c_int(splits), _ptr(sink),
         c_int(1 if values_in_keys else 0),
         _ptr(cells.cell_k if cells is not None else None),
         _ptr(cells.cell_v if cells is not None else None),

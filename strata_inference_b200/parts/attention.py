@@ -49,7 +49,15 @@ the projection and the attention kernel, in 32-bit):
                 The cache keeps a cell per block (``KVNeed.pool``), written by the step that
                 brings the block's last position (csrc/head_prepare.cu pool_store).
 
-Worked-on heads (any of the options above) are rotated in half-split or neighbouring pairs,
+``chunk``       C > 0 (without a window): a row at position p sees the positions of its own
+                chunk, C floor(p / C) .. p; chunks are counted from the sequence's position 0,
+                however the sequence was cut into steps.
+``sink``        True: one stored number per query head (``sink``) whose exponential joins the
+                softmax's denominator; it has no key and no value and is not scaled.
+``borrows_cache``  True: the layer has no key and value projections (no such tensors); its
+                schedule entry names the run whose cached keys (rotated) and values it reads.
+
+Worked-on heads (any of the options above ``chunk``) are rotated in half-split or neighbouring pairs,
 as the position part says, and are attended to by the general kernel when a window is set.
 """
 
@@ -126,7 +134,8 @@ class Attention:
         """Whether the heads are worked on between the projection and the attention."""
         return bool(params.get("bias") or params.get("qk_norm") or params.get("value_mix")
                     or params.get("head_gate") or params.get("pool")
-                    or int(params.get("value_dim") or params["head_dim"]) != params["head_dim"])
+                    or int(params.get("value_dim") or params["head_dim"]) != params["head_dim"]
+                    or int(params["head_dim"]) % 16 != 0)      # (padded to the next 16)
 
     @staticmethod
     def tensors(params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
@@ -138,6 +147,13 @@ class Attention:
             "v_proj.weight": TensorDecl((nkv * vd, hidden)),
             "o_proj.weight": TensorDecl((hidden, nh * vd)),
         }
+        if params.get("borrows_cache"):
+            if params.get("bias") or params.get("qk_norm") or params.get("value_mix") or params.get("pool"):
+                raise ConfigError("attention: a layer that reads another's keys and values has no "
+                                  "biases, norms, mixed values or pooled blocks of its own")
+            del out["k_proj.weight"], out["v_proj.weight"]
+        if params.get("sink"):
+            out["sink"] = TensorDecl((nh,), init="norm")
         if params.get("bias"):
             out["q_proj.bias"] = TensorDecl((nh * hd,), init="norm")
             out["k_proj.bias"] = TensorDecl((nkv * hd,), init="norm")
@@ -164,6 +180,8 @@ class Attention:
         n_qkv = (nh + nkv) * hd + nkv * vd
         pieces = (Piece("q_proj.weight", 0), Piece("k_proj.weight", nh * hd),
                   Piece("v_proj.weight", (nh + nkv) * hd))
+        if params.get("borrows_cache"):       # q alone
+            n_qkv, pieces = nh * hd, pieces[:1]
         if params.get("head_gate"):       # the gates' rows behind q, k and v: one product makes all
             pieces += (Piece("g_proj.weight", n_qkv),)
         out = {
@@ -171,6 +189,8 @@ class Attention:
                                         pieces=pieces),
             "o_proj.weight": Resident((hidden, nh * vd), pieces=(Piece("o_proj.weight"),)),
         }
+        if params.get("sink"):
+            out["sink"] = Resident((nh,), torch.float32, (Piece("sink"),))
         if params.get("bias"):
             out["qkv_proj.bias"] = Resident((n_qkv,), torch.float32, (
                 Piece("q_proj.bias", 0), Piece("k_proj.bias", nh * hd),
@@ -197,6 +217,13 @@ class Attention:
         self.scale = float(params["score_scale"])
         self.softcap = float(params.get("logit_softcap") or 0.0)
         self.window = int(params.get("window") or 0)
+        self.chunk = int(params.get("chunk") or 0)
+        self.sink = weights.get("sink") if params.get("sink") else None
+        self.borrows = bool(params.get("borrows_cache"))
+        if self.chunk < 0 or (self.chunk and (self.window or params.get("pool"))):
+            raise ConfigError("attention: a chunked mask goes without a window and pooled blocks")
+        if (self.chunk or self.sink is not None) and float(params.get("logit_softcap") or 0.0):
+            raise ConfigError("attention: a chunked mask or a sink goes without a soft cap")
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ConfigError(f"attention: {self.nh} heads cannot share {self.nkv} kv heads")
         self.vd = int(params.get("value_dim") or self.hd)
@@ -223,7 +250,8 @@ class Attention:
                 raise ConfigError(f"attention: value_mix {self.value_mix!r} is not 'first' or 'mix'")
             self.lam = weights.get("value_mix.weight")
             self.head_gate = bool(params.get("head_gate"))
-            self.n_qkv = (self.nh + self.nkv) * self.hd + self.nkv * self.vd
+            self.n_qkv = self.nh * self.hd if self.borrows \
+                else (self.nh + self.nkv) * self.hd + self.nkv * self.vd
             rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
             if rotary is None:
                 raise ConfigError("attention: worked-on heads take a rotary position part (or 'none')")
@@ -241,6 +269,8 @@ class Attention:
     # ------------------------------------------------------------------
     def _longest(self, ctx, capacity: int) -> int:
         longest = (min(ctx.span or capacity, capacity)) if ctx.graph_capture else ctx.max_end
+        if self.chunk > 0:
+            return min(longest, self.chunk)
         return min(longest, self.window) if self.window > 0 else longest
 
     def _splits(self, ctx, capacity: int) -> int:
@@ -338,8 +368,11 @@ class Attention:
         R = x.shape[0]
         nkv = self.nkv if owns_cache else 0
         view = ctx.kv(cache_entry)
-        if self.extras and not owns_cache:
-            raise ValueError("attention: worked-on heads cannot read another run's cache")
+        if self.borrows and owns_cache:
+            raise ValueError("attention: a layer without key and value projections reads another "
+                             "run's cache")
+        if self.extras and not owns_cache and (self.pool or self.value_mix):
+            raise ValueError("attention: pooled blocks and mixed values cannot read another run's cache")
         fresh = ctx.all_from_start and owns_cache
         if not fresh and view.ring_tokens > 0 and not ctx.graph_capture:
             # rows that attend over a ring must not overwrite a key that an earlier row of
@@ -367,9 +400,10 @@ class Attention:
                     raise ValueError("attention: values to mix in, but no earlier layer left any")
             native.head_prepare(proj, qkv, self.bias, self.q_gain, self.k_gain, self.qk_eps,
                                 rotary[0], rotary[1], v_first, self.lam if v_first is not None else None,
-                                ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end, view.k, view.v,
-                                view.page_table, view.page_tokens, view.ring_tokens, nh, nkv,
-                                self.hd, self.vd, hd, style=self.rope_style)
+                                ctx.row_pos, ctx.row_seq, ctx.seq_slot, ctx.seq_end,
+                                view.k if owns_cache else None, view.v if owns_cache else None,
+                                view.page_table if owns_cache else None, view.page_tokens,
+                                view.ring_tokens, nh, nkv, self.hd, self.vd, hd, style=self.rope_style)
             if self.pool:
                 native.pool_store(qkv, view, ctx, nh, nkv, hd)
             if self.value_mix == "first":
@@ -414,7 +448,9 @@ class Attention:
         tc_prompt = (fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0
                      and not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width)
                      and not (self.pool and self.softcap))
-        if (self.pool or (self.extras and self.window)) and not tc_prompt:
+        masked = self.chunk > 0 or self.sink is not None
+        tc_prompt = tc_prompt and not masked
+        if (self.pool or (self.extras and self.window) or masked) and not tc_prompt:
             # blocks before the window join the softmax: the general kernel, which reads the
             # step's own keys from the packed rows, earlier ones from the cache and the blocks'
             # cells from their store
@@ -429,8 +465,8 @@ class Attention:
                                   view.page_table if cached else None, view.page_tokens,
                                   view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
                                   ctx.seq_start, ctx.seq_row0, out, scratch, nh, self.nkv, hd,
-                                  self.scale, self.softcap, self.window, splits,
-                                  cells=view if self.pool else None)
+                                  self.scale, self.softcap, self.window, splits, sink=self.sink,
+                                  cells=view if self.pool else None, chunk=self.chunk)
         elif tc_prompt:
             extra = None
             if self.pool:
@@ -513,7 +549,9 @@ class LatentAttention:
     ``window`` (0: none), ``norm_eps``, ``position`` (a rotary part, applied to the rotated
     columns of q and to the shared key part), ``sink`` (one stored number per head whose
     exponential joins the softmax's denominator), ``head_gate`` (sigmoid(g_proj x) per head
-    on the head's output).
+    on the head's output), ``q_rank`` (r > 0: the queries pass a latent of their own,
+    q = uq_proj (rms_norm(dq_proj x) * dq_norm.weight) with r the latent's width, instead of
+    q = q_proj x; the norm is 32-bit and takes ``norm_eps``).
 
         q_h = [a_h | r_h] = q_proj x (per head);  k_h = [U_h c | rot(k_r)],  v_h = V_h c
         score_h(t, j) = (<a_h(t), U_h c(j)> + <rot(r_h(t)), rot(k_r(j))>) * score_scale
@@ -543,8 +581,13 @@ class LatentAttention:
     @classmethod
     def tensors(cls, params: Mapping, hidden: int) -> Dict[str, TensorDecl]:
         nh, qd, rd, vd, rank, _ = cls._sizes(params)
+        q_rank = int(params.get("q_rank") or 0)
+        queries = {"q_proj.weight": TensorDecl((nh * (qd + rd), hidden))} if not q_rank else {
+            "dq_proj.weight": TensorDecl((q_rank, hidden)),
+            "dq_norm.weight": TensorDecl((q_rank,), init="norm"),
+            "uq_proj.weight": TensorDecl((nh * (qd + rd), q_rank))}
         out = {
-            "q_proj.weight": TensorDecl((nh * (qd + rd), hidden)),
+            **queries,
             "dkv_proj.weight": TensorDecl((rank + rd, hidden)),
             "dkv_norm.weight": TensorDecl((rank,), init="norm"),
             "uk_proj.weight": TensorDecl((nh * qd, rank)),
@@ -561,8 +604,9 @@ class LatentAttention:
     def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
         """The query heads, the down projection and the gates as ONE matrix."""
         nh, qd, rd, vd, rank, _ = cls._sizes(params)
-        n_q = nh * (qd + rd)
-        pieces = (Piece("q_proj.weight", 0), Piece("dkv_proj.weight", n_q))
+        q_rank = int(params.get("q_rank") or 0)
+        n_q = q_rank or nh * (qd + rd)      # rows of the first piece: the queries, or their latent
+        pieces = (Piece("dq_proj.weight" if q_rank else "q_proj.weight", 0), Piece("dkv_proj.weight", n_q))
         n_in = n_q + rank + rd
         if params.get("head_gate"):
             pieces += (Piece("g_proj.weight", n_in),)
@@ -576,11 +620,19 @@ class LatentAttention:
         }
         if params.get("sink"):
             out["sink"] = Resident((nh,), torch.float32, (Piece("sink"),))
+        if q_rank:
+            out["dq_norm.gain"] = Resident((q_rank,), torch.float32, (Piece("dq_norm.weight"),))
+            out["uq_proj.weight"] = Resident((nh * (qd + rd), q_rank), pieces=(Piece("uq_proj.weight"),))
         return out
 
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
         self.nh, self.qd, self.rd, self.vd, self.rank, self.kw = self._sizes(params)
+        self.q_rank = int(params.get("q_rank") or 0)
+        if self.q_rank < 0:
+            raise ConfigError(f"latent_attention: q_rank {self.q_rank}")
+        self.q_gain = weights.get("dq_norm.gain")
+        self.w_uq = rt.cast_matrix(weights["uq_proj.weight"]) if self.q_rank else None
         self.scale = float(params["score_scale"])
         self.window = int(params.get("window") or 0)
         self.eps = float(params["norm_eps"])
@@ -631,7 +683,24 @@ class LatentAttention:
         want = max(1, (2 * self.rt.sm_count) // max(1, tiles))
         return max(1, min(want, -(-longest // 64), 128))
 
-    def _attend_expanded(self, proj: torch.Tensor, ctx, view) -> torch.Tensor:
+    def _project(self, x: torch.Tensor):
+        """(rows that begin with the query heads, the down projection's rows where they do not
+        follow the query heads or None, the gates' columns or None)."""
+        rt, tail = self.rt, self.rank + self.rd
+        first = rt.linear(x, self.w_in)
+        rt.flush()
+        if not self.q_rank:
+            gate = first[:, self.n_q + tail:self.n_q + tail + self.nh] if self.head_gate else None
+            return first, None, gate
+        # the queries' own latent: normed in 32-bit, then up to the heads
+        cq = torch.empty((x.shape[0], self.q_rank), dtype=first.dtype, device=first.device)
+        native.rms_norm(first[:, :self.q_rank], self.q_gain, self.eps, cq)
+        q = rt.linear(cq, self.w_uq)
+        rt.flush()
+        at = self.q_rank + tail
+        return q, first[:, self.q_rank:at], first[:, at:at + self.nh] if self.head_gate else None
+
+    def _attend_expanded(self, proj: torch.Tensor, down, gate, ctx, view) -> torch.Tensor:
         """Long prompts in bfloat16: the latent rows are normed, rotated and cached as ever, and
         for the step's own rows keys and values are made per head (k_h = U_h c, v_h = V_h c:
         two library products) and attended over by the tcgen05 prompt kernel, with the sink as
@@ -642,7 +711,7 @@ class LatentAttention:
         k_rows = torch.empty((R, kw), dtype=proj.dtype, device=proj.device)
         native.latent_prepare(proj, None, None, k_rows, self.c_gain, self.eps, self.inv_freq, self.rot,
                               ctx, view.k, view.page_table, view.page_tokens, view.ring_tokens, nh, qd, rd,
-                              rank, kw)
+                              rank, kw, down)
         c_rows = k_rows[:, :rank]
         with native.profile_region("library product (latent rows to keys and values)",
                                    (nh * (qd + vd) * rank + R * (rank + nh * (qd + vd))) * proj.element_size(),
@@ -664,7 +733,6 @@ class LatentAttention:
                                     hw, self.scale, 0.0, self.window, rt.scratch(need) if need else None,
                                     rt.tickets(n_tickets) if need else None, lens, sink=self.sink)
         vals = torch.empty((R, nh * vd), dtype=out.dtype, device=out.device)
-        gate = proj[:, self.n_q + rank + rd:self.n_q + rank + rd + nh] if self.head_gate else None
         native.head_gate(out, gate, vals, nh, vd, hw)
         return rt.linear(vals, self.w_o)
 
@@ -684,12 +752,11 @@ class LatentAttention:
                         f"a step may add at most {max(room, view.ring_tokens - start)} positions "
                         f"to a sequence of {start} whose layers keep a window of {self.window} "
                         f"in a ring of {view.ring_tokens}; got {n}")
-        proj = rt.linear(x, self.w_in)
-        rt.flush()
+        proj, down, gate = self._project(x)
         if (fresh and proj.dtype == torch.bfloat16 and _USE_LATENT_EXPAND and _USE_TCGEN05_PREFILL
                 and self.hw and self.scale > 0 and ctx.max_count > rt.short_prompt_tokens
                 and native.attention_prefill_tc_supports(nh, nh, self.hw, 3 * nh * self.hw)):
-            return self._attend_expanded(proj, ctx, view)
+            return self._attend_expanded(proj, down, gate, ctx, view)
         # the unrotated query columns of every head into the latent's space: [heads, rows, rank]
         q_heads = proj[:, :self.n_q].view(R, nh, qd + rd)[:, :, :qd].transpose(0, 1)
         with native.profile_region("library product (queries into the latent space)",
@@ -700,7 +767,7 @@ class LatentAttention:
         k_rows = torch.empty((R, kw), dtype=proj.dtype, device=proj.device)
         native.latent_prepare(proj, q_lat, q_rows, k_rows, self.c_gain, self.eps, self.inv_freq,
                               self.rot, ctx, view.k, view.page_table, view.page_tokens,
-                              view.ring_tokens, nh, qd, rd, rank, kw)
+                              view.ring_tokens, nh, qd, rd, rank, kw, down)
         out = torch.empty((R, nh * kw), dtype=proj.dtype, device=proj.device)
         tensor_cores = (proj.dtype == torch.bfloat16 and _USE_LATENT_MMA
                         and native.attention_latent_supports(nh, kw))
@@ -733,7 +800,6 @@ class LatentAttention:
                                   values_in_keys=True)
         # the heads' summed latents (gated), then V_h per head
         lat = torch.empty((R, nh * rank), dtype=out.dtype, device=out.device)
-        gate = proj[:, self.n_q + rank + rd:self.n_q + rank + rd + nh] if self.head_gate else None
         native.head_gate(out, gate, lat, nh, rank, kw)
         with native.profile_region("library product (summed latents to values)",
                                    (nh * self.vd * rank + R * nh * (self.vd + rank)) * out.element_size(),

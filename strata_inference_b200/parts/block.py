@@ -7,7 +7,10 @@ before the add, as in src/model/layer.rs:1101-1192):
     h += post_mixer(mixer(pre_mixer(h)))
     h += post_feed_forward(feed_forward(pre_feed_forward(h)))
 
-``pre_norm`` is the same arrangement without the two post norms.  A layer without a
+``pre_norm`` is the same arrangement without the two post norms.  ``residual_scale`` m (a
+block parameter, 1 unless a layer names it): what a sub-layer adds is multiplied by m,
+h += m * post(sublayer(pre(h))); the Dynamic Tanh residual kernel and the unfused steps take
+it.  A layer without a
 feed-forward (``feed_forward`` None) has the first line only.  A site whose norm is the
 ``identity`` norm passes the stream's rows on as they are, which gives the arrangement
 that norms a sub-layer's output only: h += post(sublayer(h)).  The
@@ -50,7 +53,9 @@ class SandwichBlock:
     norm_sites = ("pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward")
     required_sites = ("pre_mixer", "pre_feed_forward")
 
-    def __init__(self, mixer, feed_forward, norms: Mapping[str, object], rt):
+    def __init__(self, mixer, feed_forward, norms: Mapping[str, object], rt,
+                 residual_scale: float = 1.0):
+        self.residual_scale = float(residual_scale)
         for site in self.required_sites:
             if norms.get(site) is None and (feed_forward is not None or site == "pre_mixer"):
                 raise ConfigError(f"block: the '{site}' norm is required")
@@ -73,7 +78,7 @@ class SandwichBlock:
         deferred results through the runtime and ``kernels.native`` only, and its norms are
         the kind the residual kernel applies."""
         norms = (self.pre_mixer, self.post_mixer, self.pre_ff, self.post_ff)
-        return (getattr(self.mixer, "chain_safe", False)
+        return (self.residual_scale == 1.0 and getattr(self.mixer, "chain_safe", False)
                 and getattr(self.feed_forward, "chain_safe", False)
                 and all(_fusable(n) and (n is None or n.gain is not None) for n in norms))
 
@@ -87,8 +92,8 @@ class SandwichBlock:
                      or getattr(self.feed_forward, "captures_prompts", False)))
 
     def _add_then_norm(self, y: torch.Tensor, post, h: torch.Tensor, nxt) -> Optional[torch.Tensor]:
-        """h += post(y) (or y); returns nxt(h) if nxt is given."""
-        if _fusable(post) and _fusable(nxt):
+        """h += residual_scale * post(y) (or y); returns nxt(h) if nxt is given."""
+        if _fusable(post) and _fusable(nxt) and self.residual_scale == 1.0:
             out = torch.empty_like(y) if nxt is not None else None
             self.rt.add_rms_norm(y, post.gain if post is not None else None,
                                  post.eps if post is not None else 0.0, h,
@@ -100,12 +105,12 @@ class SandwichBlock:
             self.rt.flush()
             out = torch.empty_like(y) if nxt is not None else None
             native.add_dyt_norm(y, post.triple if post is not None else None, h,
-                                nxt.triple if nxt is not None else None, out)
+                                nxt.triple if nxt is not None else None, out, self.residual_scale)
             return out
         self.rt.flush()         # the steps below read y and h outside the chain
         if post is not None:
             y = post.forward(y, out_dtype=torch.float32)
-        h.add_(y.to(torch.float32))
+        h.add_(y.to(torch.float32), alpha=self.residual_scale)
         return nxt.forward(h, out_dtype=self.rt.dtype) if nxt is not None else None
 
     def forward(self, h: torch.Tensor, normed: Optional[torch.Tensor], ctx, entry: int,

@@ -33,6 +33,11 @@ the recurrence besides the projections (unit norms, decays, gates, the state) is
         q, k rotated by the token's position;  k <- key_scale k
         S <- decay_h S + k v^T;  o = S^T q
     then per head o / rms(o) (no weight), times silu(g_proj x), and o_proj.  State: S.
+    Options, each with the behaviour above as its default: ``activation`` "silu" (q, k and v
+    pass SiLU before anything else; lightning attention feeds its recurrence so);
+    ``norm`` "joint" (the heads side by side are divided by ONE root mean square instead of
+    one per head); ``norm_weight`` True (a stored ``norm.weight``, one per head and column,
+    multiplies the normed output); ``gate`` "sigmoid" (instead of SiLU).
 
 ``state_space``  the selective state-space layer in its dual (matrix) form.  Parameters:
     ``num_heads`` H, ``value_dim`` P (a head's channels; inner = H P), ``state_dim`` N,
@@ -264,14 +269,19 @@ class Retention:
         H, kd, vd = cls._sizes(params)
         out = {name: TensorDecl((n, hidden)) for name, n in cls._in_rows(params)}
         out["o_proj.weight"] = TensorDecl((hidden, H * vd))
+        if params.get("norm_weight"):
+            out["norm.weight"] = TensorDecl((H * vd,), init="norm")
         return out
 
     @classmethod
     def resident(cls, params: Mapping, hidden: int) -> Dict[str, Resident]:
         H, kd, vd = cls._sizes(params)
         pieces, n_in = _pieces(cls._in_rows(params))
-        return {"in_proj.weight": Resident((n_in, hidden), pieces=pieces),
-                "o_proj.weight": Resident((hidden, H * vd), pieces=(Piece("o_proj.weight"),))}
+        out = {"in_proj.weight": Resident((n_in, hidden), pieces=pieces),
+               "o_proj.weight": Resident((hidden, H * vd), pieces=(Piece("o_proj.weight"),))}
+        if params.get("norm_weight"):
+            out["norm.gain"] = Resident((H * vd,), torch.float32, (Piece("norm.weight"),))
+        return out
 
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
         self.rt = rt
@@ -290,6 +300,14 @@ class Retention:
             raise ConfigError("retention: q and k are rotated in half-split pairs")
         self.w_in = rt.cast_matrix(weights["in_proj.weight"])
         self.w_o = rt.cast_matrix(weights["o_proj.weight"])
+        act, norm, gate = params.get("activation"), params.get("norm", "head"), params.get("gate", "silu")
+        if act not in (None, "silu") or norm not in ("head", "joint") or gate not in ("silu", "sigmoid"):
+            raise ConfigError(f"retention: activation {act!r}, norm {norm!r}, gate {gate!r}; known: "
+                              f"None or 'silu', 'head' or 'joint', 'silu' or 'sigmoid'")
+        self.silu_inputs = act == "silu"
+        self.joint_norm = norm == "joint"
+        self.gate_act = native.GATE_SIGMOID if gate == "sigmoid" else native.GATE_SILU
+        self.norm_gain = weights.get("norm.gain")
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(state=StateNeed((_round4(self.H * self.vd * self.kd),)))
@@ -306,12 +324,14 @@ class Retention:
         qn, kn = torch.empty((R, H * kd), **f32), torch.empty((R, H * kd), **f32)
         vc = torch.empty((R, H * vd), **f32)
         native.retention_prepare(proj, self.inv_freq, self.rot, ctx.row_pos, qn, kn, vc, H, kd, vd,
-                                 self.key_scale)
+                                 self.key_scale, self.silu_inputs)
         o = torch.empty((R, H * vd), **f32)
         native.retention_scan(qn, kn, vc, self.decay, state, o, ctx, H, kd, vd)
         y = torch.empty((R, H * vd), dtype=proj.dtype, device=x.device)
         gate = proj[:, 2 * H * kd + H * vd:2 * H * kd + 2 * H * vd]
-        native.head_norm_gate(o, None, None, gate, y, H, vd, self.eps, native.GATE_SILU)
+        # (one root mean square over all heads: the row as a single head of heads * vd columns)
+        heads, width = (1, H * vd) if self.joint_norm else (H, vd)
+        native.head_norm_gate(o, None, self.norm_gain, gate, y, heads, width, self.eps, self.gate_act)
         return rt.linear(y, self.w_o)
 
 
