@@ -160,6 +160,8 @@ def kv_bytes_per_step(engine, lengths):
         per_token = 2 * grp.need.n_kv_heads * grp.need.head_dim * grp.k.element_size()
         for n in lengths:
             seen = min(n, grp.need.window) if grp.need.window else n
+            if getattr(grp.need, "chunk", 0):
+                seen = (n - 1) % grp.need.chunk + 1                         # the row's own chunk
             if grp.need.window and getattr(grp.need, "pool", 0):
                 seen += max(0, (n - grp.need.window) // grp.need.pool)      # one cell per block
             total += len(grp.entries) * seen * per_token
@@ -512,6 +514,33 @@ def gegorax_config(size):
             "token_side": {"dim": 64}, "layers": layers}
 
 
+def besorax_config(size):
+    """Besorax at these sizes: attention over chunks of 1 024 positions with sinks, lightning
+    attention, an attention layer that reads the first one's keys and values, latent attention
+    (Vavupel's latent of 448 + 64 rotated columns, queries through a latent of 768), and the
+    same again; feed-forwards in turn dense (the other models' width, clipped and gated) and 32
+    experts of an eighth of that width of which a row uses 4, beside a shared one of half the
+    width; lightning keeps matrices of 128 x head width."""
+    width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    routed = {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": ff // 8},
+              "shared": {"ff": ff // 2}}
+    att = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+           "mask": {"size": 1024}, "rot": {"base": 1000000.0, "dims": hd // 2}}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 448, "q_rank": 768,
+           "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    light = {"heads": heads, "dim": 128, "vdim": hd, "decay": [1.0 - 2.0 ** -(5 + i % 4) for i in range(heads)]}
+    layers = []
+    for i in range(n_layers):
+        kind = ("attention", "lightning", "attention", "latent_attention")[i % 4]
+        mixer = {"attention": att, "lightning": light, "latent_attention": lat}[kind]
+        if i % 4 == 2:
+            mixer = dict(att, kv_from=i - 2)
+        layers.append({"type": kind, "mixer": mixer, "mlp": routed if i % 2 else dense})
+    return {"architecture": "Besorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "layers": layers}
+
+
 def gemma2_config_like(size):
     width, ff, heads, kv, hd, vocab, n_layers = KARUPEL_SIZES[size]
     cfg = baseline_config()
@@ -634,8 +663,11 @@ def main():
     ap.add_argument("--gegorax", action="store_true",
                     help="instead of the timed run: Gegorax beside Karupel at equal layer sizes "
                          "(--size; with --kernels also the per-kernel tables of both)")
+    ap.add_argument("--besorax", action="store_true",
+                    help="Besorax beside Vavupel at equal layer sizes: a prompt step and single-token "
+                         "steps (with --kernels the per-kernel tables of both)")
     ap.add_argument("--size", default="", choices=[""] + sorted(KARUPEL_SIZES),
-                    help="with --karupel, --vavupel or --gegorax: one of the sizes (default: all)")
+                    help="with --karupel, --vavupel, --gegorax or --besorax: one of the sizes (default: all)")
     ap.add_argument("--shape", default="2b", choices=sorted(SHAPES),
                     help="layer sizes: the 2B shape (the recorded line) or the 9B / 27B shapes")
     args = ap.parse_args()
@@ -656,6 +688,9 @@ def main():
     if args.gegorax:
         return run_karupel(args, (("gegorax", gegorax_config), ("karupel", karupel_config)),
                            "Gegorax beside Karupel")
+    if args.besorax:
+        return run_karupel(args, (("besorax", besorax_config), ("vavupel", vavupel_config)),
+                           "Besorax beside Vavupel")
     if args.karupel:
         return run_karupel(args)
     if args.kernels:

@@ -70,6 +70,10 @@ class KVNeed:
     values_in_keys: bool = False
     # P > 0: beside the positions, one key cell and one value cell per block of P positions
     pool: int = 0
+    # C > 0: a position is only ever read by the later positions of its own chunk of C (a mask
+    # of chunks); every position is kept all the same, since a run that reads this cache may
+    # cut its chunks elsewhere
+    chunk: int = 0
 
     @property
     def v_dim(self) -> int:

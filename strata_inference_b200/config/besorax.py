@@ -242,7 +242,8 @@ def besorax_spec(cfg: BesoraxConfig) -> ModelSpec:
                 "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
                 "value_dim": m["vdim"], "score_scale": m["scale"], "logit_softcap": 0.0,
                 "window": 0, "chunk": m["chunk"], "sink": True, "position": position,
-                "borrows_cache": lender is not None})
+                "borrows_cache": lender is not None,
+                "lends_cache": any(o.type == "attention" and o.mixer["kv_from"] == i for o in cfg.layers)})
             names = _ATTENTION_NAMES
         elif l.type == "latent_attention":
             mixer = PartSpec("latent_attention", {

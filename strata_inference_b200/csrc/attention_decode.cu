@@ -49,6 +49,10 @@ struct AttnDecodeArgs {
     // (1 in a single-token step): tiles of keys below them may be loaded before that kernel
     // has finished.  0: every load waits for it.
     int fresh;
+    // > 0: a row sees the positions of its own chunk of that many (first_visible)
+    int chunk;
+    // one value per query head whose exponential joins the softmax's denominator; null: none
+    const float* sink;
 };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -89,7 +93,8 @@ constexpr int MAX_SPLITS = 128;
 // NRUN runs and G * HD / 2 <= NITEM * blockDim.x.
 template <int HD, int G, int NITEM, int NRUN>
 __device__ __forceinline__ void join_runs_by_warp(const float* unit_partial, int splits,
-                                                  __nv_bfloat16* out_row, int lane) {
+                                                  __nv_bfloat16* out_row, int lane,
+                                                  const float* sink) {
     constexpr int PW = HD + 2;
     constexpr int LR = (NRUN + 31) / 32;     // runs a lane answers for
     float2 v[NITEM][NRUN], ml[NITEM][LR];
@@ -125,7 +130,8 @@ __device__ __forceinline__ void join_runs_by_warp(const float* unit_partial, int
             f[j] = ml[k][j].x == -INFINITY ? 0.f : expf(ml[k][j].x - mx);   // a run without keys
             part += f[j] * ml[k][j].y;
         }
-        const float sum = warp_sum(part);
+        float sum = warp_sum(part);
+        if (sink) sum += expf(sink[h] - mx);       // (the heads of this kv head)
         float2 a = make_float2(0.f, 0.f);
 #pragma unroll
         for (int b = 0; b < NRUN; ++b) {         // in run order; runs beyond the last weigh 0
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
     // by the kernel before this one, so this chain of dependent loads need not wait for it.
     const int pos = p.row_pos[r];
     const int slot = p.seq_slot[p.row_seq[r]];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = first_visible(pos, p.window, p.chunk);
     const int tile_lo = lo >> 4, tile_hi = pos >> 4;             // inclusive
     const int n_tiles = tile_hi - tile_lo + 1;
     const int per = (n_tiles + nw * p.splits - 1) / (nw * p.splits);
@@ -327,6 +333,7 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
             a.y += f * v.y;
         }
         if (p.splits == 1) {
+            if (p.sink) sum += expf(p.sink[kvh * G + h] - mx);
             const float inv = 1.0f / sum;
             *reinterpret_cast<__nv_bfloat162*>(out_row + h * HD + d) =
                 __floats2bfloat162_rn(a.x * inv, a.y * inv);
@@ -346,6 +353,7 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
     if (ticket_sm != p.splits - 1) return;
     __threadfence();
     const float* unit_partial = p.partial + ((size_t)r * p.n_heads + kvh * G) * p.splits * PW;
+    const float* sink_g = p.sink ? p.sink + kvh * G : nullptr;
     // Few enough runs and columns for a warp to join its columns by itself (before: maxima, a
     // barrier, one thread's loop over the runs, a barrier, the sums' loads, a barrier, a loop,
     // a barrier, then the accumulators).
@@ -353,20 +361,20 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
         constexpr int ITEMS = G * HD / 2;
         bool joined = true;
         if (WIDE && ITEMS <= 256 && p.splits <= 32)
-            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane);
+            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane, sink_g);
         else if (WIDE && ITEMS <= 256 && p.splits <= 64)
-            join_runs_by_warp<HD, G, 1, 64>(unit_partial, p.splits, out_row, lane);
+            join_runs_by_warp<HD, G, 1, 64>(unit_partial, p.splits, out_row, lane, sink_g);
         else if (WIDE && ITEMS <= 512 && p.splits <= 32)
-            join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane);
+            join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane, sink_g);
         else if (!WIDE && ITEMS <= (int)blockDim.x && p.splits <= 32)
-            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane);
+            join_runs_by_warp<HD, G, 1, 32>(unit_partial, p.splits, out_row, lane, sink_g);
         else if (!WIDE && ITEMS <= 2 * (int)blockDim.x && p.splits <= 16)
-            join_runs_by_warp<HD, G, 2, 16>(unit_partial, p.splits, out_row, lane);
+            join_runs_by_warp<HD, G, 2, 16>(unit_partial, p.splits, out_row, lane, sink_g);
         else if (!WIDE && HD == 256 && ITEMS <= 2 * (int)blockDim.x && p.splits <= 32) {
             // (only where the loop over the keys needs as many registers anyway: at smaller
             // head sizes this would cost a resident block)
             if constexpr (HD == 256)
-                join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane);
+                join_runs_by_warp<HD, G, 2, 32>(unit_partial, p.splits, out_row, lane, sink_g);
         }
         else
             joined = false;
@@ -397,6 +405,7 @@ __global__ void __launch_bounds__(WIDE ? 256 : 128) attention_decode_kernel(Attn
         const int h = threadIdx.x;
         float sum = 0.f;
         for (int b = 0; b < p.splits; ++b) sum += l_sm[h][b];        // in run order
+        if (sink_g) sum += expf(sink_g[h] - ml_sm[h][0]);
         ml_sm[h][1] = sum;
     }
     __syncthreads();
@@ -497,8 +506,10 @@ static int attention_decode(
     int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
     const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
     int head_dim, float scale, float softcap, int window, int splits, int warps, int fresh,
-    void* stream) {
+    void* stream, int chunk = 0, const float* sink = nullptr) {
     if (rows == 0) return 0;
+    SIB_REQUIRE(chunk >= 0 && (chunk == 0 || window == 0), "attention_decode: chunk=%d window=%d (a chunk "
+                "goes without a window)", chunk, window);
     SIB_REQUIRE(sib_attention_decode_supports(n_heads, n_kv, head_dim, page_tokens),
                 "attention_decode: heads=%d kv_heads=%d head_dim=%d page_tokens=%d is not a shape "
                 "this kernel takes (groups of 1, 2, 4 or 8 heads; head_dim 64, 128 or 256; pages "
@@ -521,7 +532,7 @@ static int attention_decode(
     AttnDecodeArgs p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                      (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, partial, tickets, row_pos, row_seq,
                      seq_slot, page_table, q_stride, rows, n_heads, n_kv, max_pages, page_tokens,
-                     ring_tokens, window, splits, scale, softcap, fresh};
+                     ring_tokens, window, splits, scale, softcap, fresh, chunk, sink};
     const long long blocks = (long long)rows * n_kv * splits;
     SIB_REQUIRE(blocks < (1ll << 31), "attention_decode: too many rows (%d)", rows);
     cudaStream_t s = (cudaStream_t)stream;
@@ -590,6 +601,20 @@ SIB_EXPORT int sib_attention_decode_fresh(
                             ring_tokens, row_pos, row_seq, seq_slot, out, partial, tickets, rows,
                             n_heads, n_kv, head_dim, scale, softcap, window, splits, warps, fresh,
                             stream);
+}
+
+// The same with a mask of chunks and a sink per query head (`chunk` 0 and `sink` null: neither).
+SIB_EXPORT int sib_attention_decode_masked(
+    const void* q, int q_stride, const void* k_pool, const void* v_pool, const int* page_table,
+    int max_pages, int page_tokens, int ring_tokens, const int* row_pos, const int* row_seq,
+    const int* seq_slot, void* out, float* partial, int* tickets, int rows, int n_heads, int n_kv,
+    int head_dim, float scale, float softcap, int window, int splits, int warps, int fresh,
+    int chunk, const float* sink, void* stream) {
+    SIB_REQUIRE(fresh >= 0, "attention_decode: %d fresh positions", fresh);
+    return attention_decode(q, q_stride, k_pool, v_pool, page_table, max_pages, page_tokens,
+                            ring_tokens, row_pos, row_seq, seq_slot, out, partial, tickets, rows,
+                            n_heads, n_kv, head_dim, scale, softcap, window, splits, warps, fresh,
+                            stream, chunk, sink);
 }
 
 // ---------------------------------------------------------------------------

@@ -56,6 +56,17 @@ the projection and the attention kernel, in 32-bit):
                 softmax's denominator; it has no key and no value and is not scaled.
 ``borrows_cache``  True: the layer has no key and value projections (no such tensors); its
                 schedule entry names the run whose cached keys (rotated) and values it reads.
+``lends_cache``  True: a later run reads this layer's keys and values; in a step of prompts the
+                layer leaves its packed rows for that run, which then attends over them with
+                the prompt kernel instead of row by row over the cache.
+
+A chunked mask or a sink takes these kernels: bfloat16 prompts the tcgen05 prompt kernel, to
+which every chunk of a prompt is a sequence of its own (rows of one chunk see nothing of
+another, so a chunk's rows are a causal prompt; the rotation has been applied by position
+before) and which takes the sink in its last division; rows over the cache the decode
+kernel, whose first key is the start of the row's chunk and whose joins add the sink;
+everything else (32-bit, shapes those two do not take, recorded prompt steps) the general
+kernel.
 
 Worked-on heads (any of the options above ``chunk``) are rotated in half-split or neighbouring pairs,
 as the position part says, and are attended to by the general kernel when a window is set.
@@ -220,6 +231,7 @@ class Attention:
         self.chunk = int(params.get("chunk") or 0)
         self.sink = weights.get("sink") if params.get("sink") else None
         self.borrows = bool(params.get("borrows_cache"))
+        self.lends = bool(params.get("lends_cache"))
         if self.chunk < 0 or (self.chunk and (self.window or params.get("pool"))):
             raise ConfigError("attention: a chunked mask goes without a window and pooled blocks")
         if (self.chunk or self.sink is not None) and float(params.get("logit_softcap") or 0.0):
@@ -264,7 +276,7 @@ class Attention:
         self._block_warps = tuple(int(w) for w in os.environ.get("SIB_DECODE_WARPS", "8,4,2").split(","))
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(kv=KVNeed(self.nkv, self.kw, self.window, pool=self.pool))
+        return CacheNeed(kv=KVNeed(self.nkv, self.kw, self.window, pool=self.pool, chunk=self.chunk))
 
     # ------------------------------------------------------------------
     def _longest(self, ctx, capacity: int) -> int:
@@ -297,7 +309,9 @@ class Attention:
         if self._resident_warps is None:     # what the device holds of this kernel at a time
             self._resident_warps = {w: native.attention_decode_resident_warps(self.nh, self.nkv, self.kw, w)
                                     for w in (8, 4)}
-        return decode_shape(max(1, ctx.n_rows * self.nkv), self._longest(ctx, capacity), self.window,
+        # (a chunk that does not begin at a tile's first key reaches into one tile more, as a window does)
+        edge = self.window or (self.chunk if self.chunk % 16 else 0)
+        return decode_shape(max(1, ctx.n_rows * self.nkv), self._longest(ctx, capacity), edge,
                             self._resident_warps[4], self._resident_warps[8], self._block_warps)
 
     def _pieces_pay(self, ctx) -> bool:
@@ -362,6 +376,86 @@ class Attention:
             out[r:r + n].copy_(whole[row0 + st:row0 + st + n])
             r += n
 
+    # the most chunks of a step that the prompt kernel takes as sequences
+    _MOST_CHUNKS = 16384
+
+    def _chunks(self, ctx):
+        """The chunks of a step of prompts as sequences of the prompt kernel: (first rows on
+        the device, lengths on the device, lengths on the host, the longest)."""
+        if self.chunk <= 0:
+            return ctx.seq_row0, ctx.seq_end, ctx.counts, ctx.max_count
+        memo = ctx.memo.setdefault(("chunks", self.chunk), {})
+        if not memo:
+            row0, lens, at = [], [], 0
+            for n in ctx.counts:
+                for c in range(0, n, self.chunk):
+                    row0.append(at + c)
+                    lens.append(min(self.chunk, n - c))
+                at += n
+            dev = lambda v: torch.tensor(v, dtype=torch.int32).to(ctx.row_pos.device, non_blocking=True)  # noqa: E731
+            memo.update(row0=dev(row0), lens=dev(lens), host=lens, most=max(lens))
+        return memo["row0"], memo["lens"], memo["host"], memo["most"]
+
+    def _attend_masked(self, qkv: torch.Tensor, out: torch.Tensor, ctx, view, owns_cache: bool,
+                       cache_entry: int) -> torch.Tensor:
+        """Attention with a mask of chunks and a sink per head (either may be absent)."""
+        rt, nh, nkv, hd = self.rt, self.nh, self.nkv, self.kw
+        R = qkv.shape[0]
+        bf16 = qkv.dtype == torch.bfloat16
+        full = (nh + 2 * nkv) * hd
+        prompts = ctx.all_from_start and not ctx.graph_capture
+        if self.lends and owns_cache and prompts:
+            ctx.memo[("kv_rows", cache_entry)] = qkv
+        tc = (prompts and bf16 and _USE_TCGEN05_PREFILL and self.scale > 0
+              and native.attention_prefill_tc_supports(nh, nkv, hd, full)
+              and (self.chunk <= 0 or sum(-(-n // self.chunk) for n in ctx.counts) <= self._MOST_CHUNKS))
+        if tc and not owns_cache:
+            lent = ctx.memo.get(("kv_rows", cache_entry))
+            if lent is None or lent.shape != (R, full):
+                tc = False
+            else:           # this layer's queries beside the lender's keys and values
+                packed = torch.empty((R, full), dtype=qkv.dtype, device=qkv.device)
+                packed[:, :nh * hd].copy_(qkv[:, :nh * hd])
+                packed[:, nh * hd:].copy_(lent[:, nh * hd:])
+                qkv = packed
+        if tc:
+            row0, lens, host_lens, most = self._chunks(ctx)
+            n_seqs = len(host_lens)
+            n_items, need, n_tickets = native.attention_prefill_tc_plan(host_lens, nh, nkv, hd, 0)
+            if n_items == 0:
+                host_lens = None
+                need, n_tickets = native.attention_prefill_tc_split(n_seqs, most, nh, nkv, hd)
+            return native.attention_prefill_tc(qkv, out, row0, lens, n_seqs, most, nh, nkv, hd, self.scale,
+                                               0.0, 0, rt.scratch(need) if need else None,
+                                               rt.tickets(n_tickets) if need else None, host_lens,
+                                               sink=self.sink)
+        width = qkv.shape[1]
+        cached = not (ctx.all_from_start and owns_cache)
+        if cached and bf16 and native.attention_decode_supports(nh, nkv, hd, view.page_tokens):
+            splits, warps = self._decode_shape(ctx, ctx.cache.max_seq_len)
+            scratch = tickets = None
+            if splits > 1:
+                scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+                tickets = rt.tickets(R * nkv)
+            return native.attention_decode(qkv, width, view.k, view.v, view.page_table, view.page_tokens,
+                                           view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot, out,
+                                           scratch, tickets, nh, nkv, hd, self.scale, 0.0, 0, splits, warps,
+                                           fresh=ctx.max_count if rt.early_keys else 0, chunk=self.chunk,
+                                           sink=self.sink)
+        # the general kernel: the step's own keys from the packed rows, earlier ones from the cache
+        splits = self._splits(ctx, ctx.cache.max_seq_len) if cached else 1
+        scratch = None
+        if splits > 1:
+            scratch = rt.scratch(native.attention_rows_scratch_bytes(R, nh, hd, splits))
+        own = owns_cache and not cached
+        return native.attention_rows(qkv, width, qkv[:, nh * hd:] if own else None,
+                                     qkv[:, (nh + nkv) * hd:] if own else None, width,
+                                     view.k if cached else None, view.v if cached else None,
+                                     view.page_table if cached else None, view.page_tokens,
+                                     view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
+                                     ctx.seq_start, ctx.seq_row0, out, scratch, nh, nkv, hd,
+                                     self.scale, 0.0, 0, splits, sink=self.sink, chunk=self.chunk)
+
     def forward(self, x: torch.Tensor, ctx, entry: int, cache_entry: int,
                 owns_cache: bool) -> torch.Tensor:
         rt, nh, hd = self.rt, self.nh, self.kw
@@ -385,7 +479,7 @@ class Attention:
                         f"to a sequence of {start} whose layers keep a window of {self.window} "
                         f"in a ring of {view.ring_tokens}; got {n}")
 
-        w_in = self.w_qkv if owns_cache else self.w_q
+        w_in = self.w_qkv if (owns_cache or self.borrows) else self.w_q
         rotary = self.position.rotary() if hasattr(self.position, "rotary") else None
         proj = None
         if self.extras:
@@ -448,9 +542,9 @@ class Attention:
         tc_prompt = (fresh and qkv.dtype == torch.bfloat16 and _USE_TCGEN05_PREFILL and self.scale > 0
                      and not short and native.attention_prefill_tc_supports(nh, self.nkv, hd, width)
                      and not (self.pool and self.softcap))
-        masked = self.chunk > 0 or self.sink is not None
-        tc_prompt = tc_prompt and not masked
-        if (self.pool or (self.extras and self.window) or masked) and not tc_prompt:
+        if self.chunk > 0 or self.sink is not None:
+            out = self._attend_masked(qkv, out, ctx, view, owns_cache, cache_entry)
+        elif (self.pool or (self.extras and self.window)) and not tc_prompt:
             # blocks before the window join the softmax: the general kernel, which reads the
             # step's own keys from the packed rows, earlier ones from the cache and the blocks'
             # cells from their store
@@ -465,8 +559,8 @@ class Attention:
                                   view.page_table if cached else None, view.page_tokens,
                                   view.ring_tokens, ctx.row_pos, ctx.row_seq, ctx.seq_slot,
                                   ctx.seq_start, ctx.seq_row0, out, scratch, nh, self.nkv, hd,
-                                  self.scale, self.softcap, self.window, splits, sink=self.sink,
-                                  cells=view if self.pool else None, chunk=self.chunk)
+                                  self.scale, self.softcap, self.window, splits,
+                                  cells=view if self.pool else None)
         elif tc_prompt:
             extra = None
             if self.pool:

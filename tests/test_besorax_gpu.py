@@ -460,21 +460,26 @@ def _write_model(path, cfg, weights):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_greedy_generation_through_the_generation_engine(tmp_path, dtype):
     """Several prompts through GenerationEngine.generate (its scheduler batches them): every
-    chosen token is the plain model's best, or so near it that rounding decides."""
-    from strata_inference_b200 import GenerationConfig, GenerationEngine
+    chosen token is the plain model's best, or so near it that rounding decides, given the run's
+    own history."""
+    from strata_inference_b200 import GenerationConfig, GenerationEngine, SamplingConfig
     cfg = MIXED
     w = weights_for(cfg, 21, dtype)
     path = _write_model(str(tmp_path / "m"), cfg, w)
     engine = GenerationEngine.from_dir(path, dtype=dtype, max_tokens=1024)
     reqs = prompts(cfg, [5, 47, 90, 13], seed=22)
-    outs = engine.generate(reqs, GenerationConfig(max_tokens=24))
+    outs = engine.generate(reqs, GenerationConfig(max_tokens=24, sampling=SamplingConfig(temperature=0.0)))
+    tol = {"float32": 1e-4, "bfloat16": 0.15}[dtype]
+    far = total = 0
     for p, o in zip(reqs, outs):
-        assert len(o.token_ids) == 24
+        assert len(o.token_ids) == 24 and o.stop_reason == "max_tokens"
         ref = plain_logits(cfg, w, list(p) + list(o.token_ids))
         for k, tok in enumerate(o.token_ids):
             row = ref[len(p) + k - 1]
-            slack = (1e-3 if dtype == "float32" else 0.1) * row.abs().max().item()
-            assert row[tok].item() >= row.max().item() - slack, (k, tok)
+            far += (row.max() - row[tok]).item() > tol * row.abs().max().item()
+            total += 1
+    # (bfloat16: a row whose router scores nearly tie goes to another expert than the plain model's)
+    assert far <= (0 if dtype == "float32" else 0.04 * total), f"{far} of {total} tokens lie far below the best"
 
 
 def test_trace_replay_of_a_model_folder(tmp_path):
