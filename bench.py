@@ -567,6 +567,21 @@ def unread_expert_bytes(engine, rows):
     return total
 
 
+def spread_rows(engine):
+    """Dynamic Tanh norms of a randomly drawn model as the identity's neighbour (weight 1, b 0,
+    alpha 1).  Drawn like other norm weights (around 0, spread 0.1) they turn every row into
+    nearly the same vector b, and a router then sends all rows of a step to the same experts:
+    the experts' work would be that of the worst imbalance there is."""
+    norms = [engine.model.final_norm]
+    for blk in engine.model.blocks:
+        norms += [getattr(blk, site, None) for site in ("pre_mixer", "post_mixer", "pre_ff", "post_ff")]
+    for n in norms:
+        if n is not None and hasattr(n, "alpha") and hasattr(n, "b"):
+            n.weight.fill_(1.0)
+            n.b.zero_()
+            n.alpha.fill_(1.0)
+
+
 def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
     """Two architectures at equal layer sizes (Karupel beside Gemma2; with ``--vavupel`` Vavupel
     beside Karupel): a prompt step and single-token steps, and (``--kernels``) the per-kernel
@@ -589,6 +604,8 @@ def run_karupel(args, pair=None, title="Karupel beside Gemma2"):
                                                max_slots=max(batches))
             engine = gen.engine
             randomize_pools(engine)
+            if name == "besorax":
+                spread_rows(engine)
             weight_bytes = engine.model.weight_bytes()
             row = {"weights_gb": round(weight_bytes / 1e9, 2)}
             if getattr(engine.model.head, "weight", None) is not engine.model.embedding.table:

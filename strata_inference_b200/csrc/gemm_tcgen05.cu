@@ -24,7 +24,9 @@
 #include "common.cuh"
 
 enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2, GEMM_EPI_SWIGLU = 4,
-       GEMM_EPI_RELU2 = 5 };    // (5: the square of max(y, 0), value by value)
+       GEMM_EPI_RELU2 = 5,      // (5: the square of max(y, 0), value by value)
+       GEMM_EPI_CLIPPED = 6 };  // (6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
+                                //  u = clamp(u, -cap, cap); `cap` carries the limit)
 
 static constexpr int BM = 128;        // weight rows per block
 static constexpr int BK = 64;         // k per stage: 128 bytes, one swizzle row
@@ -115,7 +117,16 @@ __device__ __forceinline__ float gemm_gate_act(float g, int epilogue) {
     return epilogue == GEMM_EPI_SWIGLU ? g / (1.0f + expf(-g)) : gemm_gelu_tanh(g);
 }
 __host__ __device__ __forceinline__ bool gemm_gated(int epilogue) {
-    return epilogue == GEMM_EPI_GEGLU || epilogue == GEMM_EPI_SWIGLU;
+    return epilogue == GEMM_EPI_GEGLU || epilogue == GEMM_EPI_SWIGLU || epilogue == GEMM_EPI_CLIPPED;
+}
+// a gate value and its up value as one output of the gated epilogues
+__device__ __forceinline__ float gemm_gated_pair(float g, float u, int epilogue, float cap) {
+    if (epilogue == GEMM_EPI_CLIPPED) {
+        g = fminf(g, cap);
+        u = fminf(fmaxf(u, -cap), cap);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return gemm_gate_act(g, epilogue) * u;
 }
 
 struct GemmArgs {
@@ -225,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const float up = __shfl_down_sync(0xffffffffu, mine, 8);
                         const int r = r0 + c0 + j;
                         if (is_gate && n + 8 < p.N && r < p.R)
-                            y[(size_t)r * p.y_stride + col] = from_f32<OutT>(gemm_gate_act(mine, p.epilogue) * up);
+                            y[(size_t)r * p.y_stride + col] = from_f32<OutT>(gemm_gated_pair(mine, up, p.epilogue, p.cap));
                     }
                 } else {
 #pragma unroll
@@ -480,8 +491,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     for (int g = 0; g < 2; ++g)
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            o[8 * g + i] = gemm_gate_act(__uint_as_float(v[16 * g + i]), p.epilogue) *
-                                           __uint_as_float(v[16 * g + 8 + i]);
+                            o[8 * g + i] = gemm_gated_pair(__uint_as_float(v[16 * g + i]),
+                                                           __uint_as_float(v[16 * g + 8 + i]), p.epilogue, p.cap);
                     OutT* dst = y + (size_t)r * p.y_stride + n / 2;
                     const int count = min(32, p.N - n) / 2;
                     if (count == 16 && ((uintptr_t)dst & 15) == 0 && sizeof(OutT) == 2) {
@@ -636,7 +647,8 @@ static int gemm_tcgen05(const void* W, const void* x, void* y, int out_dtype, in
                 "gemm_tcgen05: operands must be 16-byte aligned");
     SIB_REQUIRE(!gemm_gated(epilogue) || N % 16 == 0,
                 "gemm_tcgen05: the gated epilogue needs N (%d) in whole groups of 16", N);
-    SIB_REQUIRE(epilogue != GEMM_EPI_SOFTCAP || cap > 0.f, "gemm_tcgen05: soft cap must be positive");
+    SIB_REQUIRE((epilogue != GEMM_EPI_SOFTCAP && epilogue != GEMM_EPI_CLIPPED) || cap > 0.f,
+                "gemm_tcgen05: the soft cap (the clipped gate's limit) must be positive");
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     SIB_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, "gemm_tcgen05: no current device");

@@ -34,7 +34,9 @@
 namespace cg = cooperative_groups;
 
 enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3, EPI_SWIGLU = 4,
-       EPI_RELU2 = 5 };     // (5: the square of max(y, 0), value by value)
+       EPI_RELU2 = 5,       // (5: the square of max(y, 0), value by value)
+       EPI_CLIPPED = 6 };   // (6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
+                            //  u = clamp(u, -cap, cap); `cap` carries the limit)
 
 // What the q|k|v product needs to rotate and store (see rope_cache.cu for the cache layout).
 struct RopeTail {
@@ -80,6 +82,15 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g));
 // the gate's activation of the two gated epilogues (tanh-GELU, SiLU)
 template <int EPI> __device__ __forceinline__ float gate_act(float g) {
     return EPI == EPI_SWIGLU ? silu_f(g) : gelu_tanh_f(g);
+}
+// a gate value and its up value as one output of the gated epilogues
+template <int EPI> __device__ __forceinline__ float gated_pair(float g, float u, float cap) {
+    if (EPI == EPI_CLIPPED) {
+        g = fminf(g, cap);
+        u = fminf(fmaxf(u, -cap), cap);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return gate_act<EPI>(g) * u;
 }
 
 // NT: activation tiles of 8 rows; MT: weight tiles of 16 rows per block.
@@ -257,13 +268,13 @@ __device__ __forceinline__ void skinny_linear_body(
                     }
                 }
             }
-        } else if (EPI == EPI_GEGLU || EPI == EPI_SWIGLU) {
+        } else if (EPI == EPI_GEGLU || EPI == EPI_SWIGLU || EPI == EPI_CLIPPED) {
             // rows gg (gate) and gg + 8 (up) of the 16-row group make column n_out
             const int n_out = (n0 + 16 * m) / 2 + gg;
             if (n_lo + 8 < N) {
-                if (r0 < R) y[(size_t)r0 * y_stride + n_out] = from_f32<OutT>(gate_act<EPI>(s.x) * s.z);
+                if (r0 < R) y[(size_t)r0 * y_stride + n_out] = from_f32<OutT>(gated_pair<EPI>(s.x, s.z, cap));
                 if (r0 + 1 < R)
-                    y[(size_t)(r0 + 1) * y_stride + n_out] = from_f32<OutT>(gate_act<EPI>(s.y) * s.w);
+                    y[(size_t)(r0 + 1) * y_stride + n_out] = from_f32<OutT>(gated_pair<EPI>(s.y, s.w, cap));
             }
         } else {
             float o[4] = {s.x, s.y, s.z, s.w};
@@ -401,9 +412,10 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
                 "skinny_linear: N=%d K=%d; K must be a multiple of 8", N, K);
     SIB_REQUIRE(x_stride % 8 == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)x % 16) == 0,
                 "skinny_linear: operands must be 16-byte aligned (x_stride=%d)", x_stride);
-    SIB_REQUIRE((epilogue != EPI_GEGLU && epilogue != EPI_SWIGLU) || N % 16 == 0,
+    SIB_REQUIRE((epilogue != EPI_GEGLU && epilogue != EPI_SWIGLU && epilogue != EPI_CLIPPED) || N % 16 == 0,
                 "skinny_linear: the gated epilogue needs N (%d) in whole groups of 16", N);
-    SIB_REQUIRE(epilogue != EPI_SOFTCAP || cap > 0.f, "skinny_linear: soft cap must be positive");
+    SIB_REQUIRE((epilogue != EPI_SOFTCAP && epilogue != EPI_CLIPPED) || cap > 0.f,
+                "skinny_linear: the soft cap (the clipped gate's limit) must be positive");
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(OUT, EPI) \
     return dispatch_skinny<OUT, EPI>(W, x, y, R, N, K, x_stride, y_stride, cap, RopeTail{}, s)
@@ -413,6 +425,7 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
         if (epilogue == EPI_SWIGLU) GO(__nv_bfloat16, EPI_SWIGLU);
         if (epilogue == EPI_SOFTCAP) GO(__nv_bfloat16, EPI_SOFTCAP);
         if (epilogue == EPI_RELU2) GO(__nv_bfloat16, EPI_RELU2);
+        if (epilogue == EPI_CLIPPED) GO(__nv_bfloat16, EPI_CLIPPED);
     } else if (out_dtype == SIB_F32) {
         if (epilogue == EPI_NONE) GO(float, EPI_NONE);
         if (epilogue == EPI_SOFTCAP) GO(float, EPI_SOFTCAP);

@@ -829,6 +829,35 @@ head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ m, 
     }
 }
 
+// The same for heads of many columns (all heads normed together count as one): a block per
+// (row, head), its threads sharing the columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+wide_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ m, const float* __restrict__ w,
+                      int w_stride, const T* __restrict__ gate, long long gate_stride,
+                      T* __restrict__ y, int H, int vd, int cols, float eps, int act) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const size_t unit = blockIdx.x;
+    const size_t r = unit / H;
+    const int h = (int)(unit % H);
+    const float* x = o + unit * cols;
+    float scale = 1.f;
+    if (m) scale = 1.0f / (fmaxf(fabsf(x[vd]), expf(-m[unit])) + 1e-6f);
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < vd; e += blockDim.x) {
+        const float v = x[e] * scale;
+        ss += v * v;
+    }
+    const float inv = scale / sqrtf(block_sum(ss, scratch) / (float)vd + eps);
+    for (int e = threadIdx.x; e < vd; e += blockDim.x) {
+        const float z = to_f32(gate[r * gate_stride + (size_t)h * vd + e]);
+        const float a = act == 0 ? silu_f(z) : sigmoid_f(z);
+        y[unit * vd + e] = from_f32<T>(x[e] * inv * (w ? w[(size_t)h * w_stride + e] : 1.0f) * a);
+    }
+}
+
 SIB_EXPORT int sib_head_norm_gate(const float* o, const float* m, const float* w, int w_stride,
                                   const void* gate, long long gate_stride, void* y, int dtype,
                                   int rows, int H, int vd, int cols, float eps, int act,
@@ -837,7 +866,13 @@ SIB_EXPORT int sib_head_norm_gate(const float* o, const float* m, const float* w
     SIB_REQUIRE(rows > 0 && H > 0 && vd > 0 && cols >= vd && (m == nullptr || cols > vd),
                 "head_norm_gate: rows=%d heads=%d width=%d of %d", rows, H, vd, cols);
     const long long blocks = ((long long)rows * H + 3) / 4;
-    SIB_REQUIRE(blocks < (1ll << 31), "head_norm_gate: too many rows (%d)", rows);
+    SIB_REQUIRE(blocks < (1ll << 29), "head_norm_gate: too many rows (%d)", rows);
+    if (vd >= 512) {
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(wide_norm_gate_kernel<T>, dim3((unsigned)((long long)rows * H)),
+                                                     dim3(256), 0, (cudaStream_t)stream, o, m, w, w_stride,
+                                                     (const T*)gate, gate_stride, (T*)y, H, vd, cols, eps, act));
+        return sib_check_launch("head_norm_gate");
+    }
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(head_norm_gate_kernel<T>, dim3((unsigned)blocks),
                                                  dim3(128), 0, (cudaStream_t)stream, o, m, w, w_stride,
                                                  (const T*)gate, gate_stride, (T*)y, rows, H, vd, cols,

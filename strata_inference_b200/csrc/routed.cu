@@ -122,10 +122,12 @@ router_rows_kernel(const T* __restrict__ x, long long x_stride, const float* __r
         choose_top(z, bias, ids + (size_t)r * top, weights + (size_t)r * top, experts, top, lane, score);
 }
 
+// `group` 8: gate and up columns lie interleaved in eights (8 gates, then their 8 ups), as the
+// products with a gated epilogue keep their matrices; 0: all gates, then all ups.
 template <typename T>
 __global__ void expert_activate_kernel(const T* __restrict__ gu, long long stride, T* __restrict__ y,
                                        const float* __restrict__ row_weight, int ff, float limit,
-                                       float alpha, size_t total, int form) {
+                                       float alpha, size_t total, int form, int group) {
     pdl_trigger();
     pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -136,10 +138,56 @@ __global__ void expert_activate_kernel(const T* __restrict__ gu, long long strid
         if (form == FORM_PLAIN_GELU) {       // rows [up (ff)]; the row's weight on what enters the gelu
             v = gelu_erf(to_f32(gu[r * stride + j]) * (row_weight ? row_weight[r] : 1.0f));
         } else {
-            v = expert_act(to_f32(gu[r * stride + j]), to_f32(gu[r * stride + ff + j]), limit, alpha);
+            const size_t g = group ? (size_t)(j / group) * 2 * group + j % group : (size_t)j;
+            v = expert_act(to_f32(gu[r * stride + g]), to_f32(gu[r * stride + g + (group ? group : ff)]), limit, alpha);
             if (row_weight) v *= row_weight[r];
         }
         y[i] = from_f32<T>(v);
+    }
+}
+
+// The same for bfloat16 rows whose widths are multiples of 8 and start on 16-byte boundaries: a
+// thread takes 8 neighbouring outputs, whose gates and ups are 16 bytes each in either layout.
+__global__ void expert_activate8_kernel(const __nv_bfloat16* __restrict__ gu, long long stride,
+                                        __nv_bfloat16* __restrict__ y, const float* __restrict__ row_weight,
+                                        int ff, float limit, float alpha, size_t total8, int form, int group) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = ff / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / per_row;
+        const int j = (int)(i - r * per_row) * 8;
+        const float rw = row_weight ? row_weight[r] : 1.0f;
+        float o[8];
+        if (form == FORM_PLAIN_GELU) {
+            const uint4 a = *reinterpret_cast<const uint4*>(gu + r * stride + j);
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[2 * e] = gelu_erf(__uint_as_float(w[e] << 16) * rw);
+                o[2 * e + 1] = gelu_erf(__uint_as_float(w[e] & 0xffff0000u) * rw);
+            }
+        } else {
+            const size_t g = group ? (size_t)2 * j : (size_t)j;
+            const uint4 a = *reinterpret_cast<const uint4*>(gu + r * stride + g);
+            const uint4 b = *reinterpret_cast<const uint4*>(gu + r * stride + g + (group ? 8 : ff));
+            const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[2 * e] = expert_act(__uint_as_float(wa[e] << 16), __uint_as_float(wb[e] << 16), limit, alpha) * rw;
+                o[2 * e + 1] = expert_act(__uint_as_float(wa[e] & 0xffff0000u), __uint_as_float(wb[e] & 0xffff0000u),
+                                          limit, alpha) * rw;
+            }
+        }
+        uint4 out;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 pr = __floats2bfloat162_rn(o[2 * e], o[2 * e + 1]);
+            ow[e] = *reinterpret_cast<const uint32_t*>(&pr);
+        }
+        *reinterpret_cast<uint4*>(y + r * ff + j) = out;
     }
 }
 
@@ -444,14 +492,23 @@ SIB_EXPORT int sib_router_rows(const void* x, long long x_stride, int dtype, con
 
 SIB_EXPORT int sib_expert_activate(const void* gu, long long stride, void* y, const float* row_weight,
                                    int dtype, int rows, int ff, float limit, float alpha, int form,
-                                   void* stream) {
+                                   int group, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && ff > 0 && stride >= (form == FORM_PLAIN_GELU ? 1 : 2) * ff,
                 "expert_activate: rows=%d ff=%d", rows, ff);
+    SIB_REQUIRE(group == 0 || (group == 8 && ff % 8 == 0 && form != FORM_PLAIN_GELU),
+                "expert_activate: columns interleaved in groups of %d (0 or 8, ff a multiple of 8)", group);
     const size_t total = (size_t)rows * ff;
+    if (dtype == SIB_BF16 && ff % 8 == 0 && stride % 8 == 0 && ((uintptr_t)gu % 16) == 0 &&
+        ((uintptr_t)y % 16) == 0) {
+        sib_launch_chained(expert_activate8_kernel, dim3(grid_for(total / 8)), dim3(256), 0,
+                           (cudaStream_t)stream, (const __nv_bfloat16*)gu, stride, (__nv_bfloat16*)y, row_weight,
+                           ff, limit, alpha, total / 8, form, group);
+        return sib_check_launch("expert_activate");
+    }
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(expert_activate_kernel<T>, dim3(grid_for(total)),
                                                  dim3(256), 0, (cudaStream_t)stream, (const T*)gu,
-                                                 stride, (T*)y, row_weight, ff, limit, alpha, total, form));
+                                                 stride, (T*)y, row_weight, ff, limit, alpha, total, form, group));
     return sib_check_launch("expert_activate");
 }
 
@@ -484,8 +541,11 @@ SIB_EXPORT int sib_routed_rows(const void* x, long long x_stride, const void* w_
     }
     int rc = sib_check_launch("routed_rows_gate_up");
     if (rc) return rc;
+    // (few rows: more blocks a row, so that the device is filled twice over: with one row and 64
+    // blocks a warp walked 8 output columns one after the other, 100 us a layer at width 2 048)
+    const int down_tiles = min((width + 3) / 4, max(64, 1184 / rows));
     SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(routed_rows_down_kernel<T>,
-                                                 dim3(min((width + 3) / 4, 64), rows), dim3(128),
+                                                 dim3(down_tiles, rows), dim3(128),
                                                  (size_t)top * ff * 4, s, (const T*)mid,
                                                  (const T*)w_down, ids, out_weights, (const T*)base,
                                                  (T*)out, width, ff, top));

@@ -21,7 +21,10 @@ F32, BF16 = 0, 1
 EPI_NONE, EPI_SOFTCAP, EPI_GEGLU = 0, 1, 2
 EPI_SWIGLU = 4          # the gated epilogue with SiLU (weight-streaming and paired tcgen05 products)
 EPI_RELU2 = 5           # the square of max(y, 0), value by value (the same two products)
-GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU)
+# the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap), u = clamp(u, -cap, cap): the
+# products' ``cap`` carries the limit (the same two products)
+EPI_CLIPPED = 6
+GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU, EPI_CLIPPED)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
 ACT_RELU_SQUARED = 2                    # of the feed-forward without a gate (activate)
@@ -554,11 +557,12 @@ def router_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
 
 @_timed(lambda gu, y, row_weight, limit, alpha, *a: ("expert_activate", _nbytes(gu, y), 0))
 def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torch.Tensor],
-                    limit: float, alpha: float, form: int = FORM_CLIPPED_GATED) -> torch.Tensor:
+                    limit: float, alpha: float, form: int = FORM_CLIPPED_GATED,
+                    group: int = 0) -> torch.Tensor:
     """FORM_CLIPPED_GATED: y = g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up,
     -limit, limit), from rows ``[gate (ff) | up (ff)]``; with ``row_weight`` every row times its
     32-bit weight.  FORM_PLAIN_GELU: y = gelu(row_weight * up), the exact gelu, from rows ``[up
-    (ff)]``."""
+    (ff)]``.  ``group`` 8: gates and ups lie interleaved in eights (8 gates, then their 8 ups)."""
     rows, ff = y.shape
     _want(gu, y.dtype, "gu", contiguous=False)
     _want(y, y.dtype, "y")
@@ -568,7 +572,7 @@ def expert_activate(gu: torch.Tensor, y: torch.Tensor, row_weight: Optional[torc
         _f32(row_weight, rows, "row_weight")
     _check(library().sib_expert_activate(_ptr(gu), c_longlong(gu.stride(0)), _ptr(y), _ptr(row_weight),
                                          _code(y.dtype), c_int(rows), c_int(ff), c_float(limit),
-                                         c_float(alpha), c_int(form), _stream()))
+                                         c_float(alpha), c_int(form), c_int(group), _stream()))
     return y
 
 

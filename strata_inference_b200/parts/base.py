@@ -207,7 +207,7 @@ class Runtime:
         n_out = N // 2 if gated else N
         # (the chain kernel, the staged product and the tcgen05 weight-streaming product know
         # the tanh-GELU gate only)
-        only_gelu = epilogue not in (native.EPI_SWIGLU, native.EPI_RELU2)
+        only_gelu = epilogue not in (native.EPI_SWIGLU, native.EPI_RELU2, native.EPI_CLIPPED)
         if self._chainable(x, w, out_dtype) and only_gelu and (out_dtype == torch.bfloat16
                                                                or not gated):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)

@@ -30,8 +30,9 @@ experts have no biases, up(p x) = p up(x), so the weight is applied in 32-bit to
 product's output in front of the gelu.
 Few rows, and every recorded step: each (row, expert) pair streams its expert's matrices
 (csrc/routed.cu routed_rows).  Many rows: the pairs are sorted by expert on the device into a
-layout [experts, most rows of any expert, width] (that one number is read on the host) and all
-experts run as two batched library products around one activation launch.
+layout [experts, most rows of any expert, width] (that one number is read on the host; a recorded
+step takes its number of rows instead and reads nothing) and all experts run as two batched library
+products around one activation launch.
 """
 
 from __future__ import annotations
@@ -163,10 +164,17 @@ class ClippedGatedMLP:
 
     @staticmethod
     def resident(params: Mapping, hidden: int) -> Dict[str, Resident]:
-        """Gate and up as ONE matrix (all gate rows, then all up rows): one product makes both."""
+        """Gate and up as ONE matrix, laid out as the gated feed-forward's: runs of 8 gate rows
+        followed by the 8 matching up rows when the intermediate size is a multiple of 8 (the
+        products' clipped epilogue then writes the activated middle itself), else all gates,
+        then all ups."""
         inter = int(params["intermediate_size"])
-        return {"gate_up_proj.weight": Resident((2 * inter, hidden), pieces=(
-                    Piece("gate_proj.weight", 0), Piece("up_proj.weight", inter))),
+        if inter % _GROUP == 0:
+            pieces = (Piece("gate_proj.weight", 0, _GROUP, 2 * _GROUP),
+                      Piece("up_proj.weight", _GROUP, _GROUP, 2 * _GROUP))
+        else:
+            pieces = (Piece("gate_proj.weight", 0), Piece("up_proj.weight", inter))
+        return {"gate_up_proj.weight": Resident((2 * inter, hidden), pieces=pieces),
                 "down_proj.weight": Resident((hidden, inter), pieces=(Piece("down_proj.weight"),))}
 
     def __init__(self, params: Mapping, hidden: int, weights: Mapping[str, torch.Tensor], rt):
@@ -180,11 +188,18 @@ class ClippedGatedMLP:
         self.w_down = rt.cast_matrix(weights["down_proj.weight"])
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gu = self.rt.linear(x, self.w_gate_up)
-        self.rt.flush()
-        mid = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        native.expert_activate(gu, mid, None, self.limit, self.alpha)
-        return self.rt.linear(mid, self.w_down)
+        rt, R = self.rt, x.shape[0]
+        group = _GROUP if self.inter % _GROUP == 0 else 0
+        # (the products' epilogue has the design's constant 1.702 built in)
+        if (group and self.alpha == 1.702 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and (R <= rt.skinny_max_rows or R > rt.gated_gemm_min_rows)):
+            mid = rt.linear(x, self.w_gate_up, epilogue=native.EPI_CLIPPED, cap=self.limit)
+        else:
+            gu = rt.linear(x, self.w_gate_up)
+            rt.flush()
+            mid = torch.empty((R, self.inter), dtype=x.dtype, device=x.device)
+            native.expert_activate(gu, mid, None, self.limit, self.alpha, native.FORM_CLIPPED_GATED, group)
+        return rt.linear(mid, self.w_down)
 
 
 _FORMS = {"clipped_gated": native.FORM_CLIPPED_GATED, "plain_gelu": native.FORM_PLAIN_GELU}
@@ -310,7 +325,7 @@ class RoutedExperts:
             native.expert_activate(gu, mid, None, self.shared_limit, self.alpha, self.form)
             base = rt.linear(mid, self.w_sdown)
         out = torch.empty((R, self.hidden), dtype=x.dtype, device=x.device)
-        if ctx.graph_capture or R <= self.pair_rows:
+        if R <= self.pair_rows:
             return native.routed_rows(x, self.w_gu, self.w_down, ids, p, base, out, self.limit, self.alpha,
                                       self.form)
         # The pairs sorted by expert and laid out [experts, most, width] with `most` the largest
@@ -318,11 +333,16 @@ class RoutedExperts:
         # expert's own are zeros): all experts run as ONE batched library product for gate and
         # up, one activation launch and one batched product for down.  `where[r, k]`: the
         # place of row r's k-th pair in that layout.
+        # A recorded step reads nothing on the host: every expert gets room for all the step's
+        # rows (an expert is chosen at most once a row).  For the 33 to 64 rows of such a step
+        # that is a few products' worth of zeros on the tensor cores, against the streamed
+        # kernels' sums on the CUDA cores (64 rows of 4 experts each: 558 us a layer).
         E, top, W = self.E, self.top, self.hidden
         flat = ids.view(-1).to(torch.int64)
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=E)
-        most = int(counts.max().item())
+        counts = torch.zeros(E, dtype=torch.int64, device=x.device).index_add_(
+            0, flat, torch.ones_like(flat))
+        most = R if ctx.graph_capture else int(counts.max().item())
         most = -(-most // 8) * 8
         by_expert = flat[order]
         place = by_expert * most + (torch.arange(order.numel(), device=x.device)

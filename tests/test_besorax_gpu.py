@@ -341,6 +341,23 @@ def test_many_rows_choose_their_experts(dtype):
     assert_close(run_portions(eng, toks, [300, 33, 20, 8, 5] + [1] * 34), ref, dtype, "fewer and fewer rows")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_recorded_steps_of_many_rows_choose_their_experts(dtype):
+    """48 requests decoded together: their single-token steps are recorded and replayed, and the
+    experts of so many rows run as batched products with room for every row at every expert."""
+    cfg = model(64, 120, [lightning(2, 16, 16, [0.9, 0.99], mlp=moe(6, 3, 24, shared=16)),
+                          attention(2, 1, 16, 16, 20, mlp=moe(5, 1, 40))])
+    w = weights_for(cfg, 52, dtype)
+    eng = make_engine(cfg, w, dtype, max_tokens=4096, max_slots=48)
+    reqs = prompts(cfg, [9 + (i * 7) % 23 for i in range(48)], seed=53)
+    refs = [plain_logits(cfg, w, t) for t in reqs]
+    slots = [eng.new_sequence() for _ in reqs]
+    eng.step([(s, t[:4]) for s, t in zip(slots, reqs)], [[3]] * 48)
+    for k in range(4, 9):
+        out = eng.step([(s, [t[k]]) for s, t in zip(slots, reqs)], [[0]] * 48)
+        assert_close(out, torch.stack([r[k] for r in refs]), dtype, f"48 requests, token {k}")
+
+
 # --------------------------------------------------------------------------
 # kernels alone, against plain functions
 
@@ -425,6 +442,173 @@ def test_general_attention_kernel_with_chunks_and_sinks(chunk, heads, kv, hd, dt
             want[r, a] = plain.softmax_with_sink(s, float(sink[a])) @ v[r0 + lo:r0 + t + 1, gq]
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert np.abs(out.float().cpu().numpy().reshape(R, heads, hd) - want).max() <= tol
+
+
+def _chunked_reference(q, k, v, sink, scale, chunk):
+    """q[T, H, d], k and v [T, G, d] of one sequence (bfloat16 values): rows of a 64-bit softmax
+    over the row's own chunk with the sink in the denominator."""
+    T, H, d = q.shape
+    G = k.shape[1]
+    q, k, v = (x.double().numpy() for x in (q, k, v))
+    out = np.zeros((T, H, d))
+    for t in range(T):
+        lo = plain.visible_from(t, chunk)
+        for a in range(H):
+            s = (k[lo:t + 1, a // (H // G)] @ q[t, a]) * scale
+            out[t, a] = plain.softmax_with_sink(s, None if sink is None else float(sink[a])) @ v[lo:t + 1, a // (H // G)]
+    return out
+
+
+@pytest.mark.parametrize("nh, nkv, hd, chunk, splits, warps", [
+    (4, 2, 128, 96, 1, 4), (4, 2, 128, 96, 3, 4), (8, 1, 64, 40, 5, 2), (2, 2, 256, 16, 2, 8), (8, 4, 256, 100, 20, 4),
+    (16, 2, 64, 7, 1, 1), (4, 4, 128, 1, 2, 4), (8, 2, 128, 1000, 40, 8), (2, 1, 128, 33, 70, 8)])
+def test_decode_kernel_with_chunks_and_sinks(nh, nkv, hd, chunk, splits, warps):
+    """The bfloat16 decode kernel over a paged cache whose pages lie in any order: rows at the
+    first and last positions of chunks, at tile and page borders; sinks far above and far below
+    the scores; every way of joining the runs."""
+    from strata_inference_b200.kernels import native
+    assert native.attention_decode_supports(nh, nkv, hd, 16)
+    g = torch.Generator().manual_seed(nh * hd + chunk)
+    T, page = 230, 16
+    q = torch.randn((T, nh, hd), generator=g).to(torch.bfloat16)
+    k = torch.randn((T, nkv, hd), generator=g).to(torch.bfloat16)
+    v = torch.randn((T, nkv, hd), generator=g).to(torch.bfloat16)
+    sink = torch.randn(nh, generator=g) * 4.0 + 1.0
+    scale = 3.0 / math.sqrt(hd)
+    ref = _chunked_reference(q, k, v, sink, scale, chunk)
+    n_pages = -(-T // page)
+    order = torch.randperm(n_pages + 3, generator=g)[:n_pages]
+    kp = torch.full((n_pages + 3, nkv, page, hd), 1e4, dtype=torch.bfloat16)      # (loud if read)
+    vp = torch.full((n_pages + 3, nkv, page, hd), 1e4, dtype=torch.bfloat16)
+    for t in range(T):
+        kp[order[t // page], :, t % page], vp[order[t // page], :, t % page] = k[t], v[t]
+    table = torch.zeros((2, n_pages), dtype=torch.int32)
+    table[1] = order.to(torch.int32)
+    edges = {0, 1, 15, 16, 17, T - 1}
+    for c in range(0, T, max(chunk, 1)):
+        edges |= {c, c + 1, c + chunk - 1, c + chunk // 2}
+    rows = sorted(r for r in edges if 0 <= r < T)[:40]
+    R = len(rows)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+    qs = torch.stack([q[r].reshape(nh * hd) for r in rows]).contiguous().cuda()
+    out = torch.empty((R, nh * hd), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty(max(1, native.attention_rows_scratch_bytes(R, nh, hd, splits)), dtype=torch.uint8, device="cuda")
+    tickets = torch.zeros(R * nkv, dtype=torch.int32, device="cuda")
+    native.attention_decode(qs, nh * hd, kp.cuda(), vp.cuda(), table.cuda(), page, 0, i32(rows), i32([0] * R), i32([1]),
+                            out, scratch, tickets, nh, nkv, hd, scale, 0.0, 0, splits, warps, chunk=chunk, sink=sink.cuda())
+    assert int(tickets.abs().sum()) == 0, "the ticket counters are put back"
+    got = out.float().cpu().numpy().reshape(R, nh, hd)
+    for i, r in enumerate(rows):
+        err = np.abs(got[i] - ref[r]).max()
+        assert err <= 2e-2 * max(1.0, np.abs(ref[r]).max()), f"row at position {r}: {err:.3e}"
+
+
+@pytest.mark.parametrize("heads, kv, hd, chunk, lens", [(4, 2, 128, 96, [398, 23, 97]), (4, 4, 64, 40, [200, 5, 64, 131]),
+                                                        (2, 1, 256, 128, [700, 130]), (8, 4, 128, 1, [50]),
+                                                        (2, 2, 128, 5000, [1500]), (6, 3, 64, 0, [300, 90])])
+def test_prompt_kernel_over_chunks_with_sinks(heads, kv, hd, chunk, lens):
+    """The tcgen05 prompt kernel with every chunk of a prompt as a sequence of its own and a sink
+    per head, against the 64-bit softmax over the row's chunk: as a grid and as a balanced list."""
+    from strata_inference_b200.kernels import native
+    if not native.attention_prefill_tc_supports(heads, kv, hd, (heads + 2 * kv) * hd):
+        pytest.skip("not a shape of the prompt kernel")
+    g = torch.Generator().manual_seed(heads + hd + chunk)
+    scale = 3.0 / math.sqrt(hd)
+    sink = torch.randn(heads, generator=g) * 3.0 + 2.0
+    rows, refs, row0, sizes, at = [], [], [], [], 0
+    for T in lens:
+        q = torch.randn((T, heads, hd), generator=g).to(torch.bfloat16)
+        k, v = (torch.randn((T, kv, hd), generator=g).to(torch.bfloat16) for _ in range(2))
+        refs.append(_chunked_reference(q, k, v, sink, scale, chunk))
+        rows.append(torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=1))
+        step = chunk or T
+        for c in range(0, T, step):
+            row0.append(at + c)
+            sizes.append(min(step, T - c))
+        at += T
+    packed = torch.cat(rows).contiguous().cuda()
+    ref = np.concatenate(refs).reshape(sum(lens), -1)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")  # noqa: E731
+
+    def run(scratch, tickets, host):
+        out = torch.full((sum(lens), heads * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        native.attention_prefill_tc(packed, out, i32(row0), i32(sizes), len(sizes), max(sizes), heads, kv, hd, scale,
+                                    0.0, 0, scratch, tickets, host, sink=sink.cuda())
+        assert native.attention_prefill_tc_error() == 0
+        err = np.abs(out.float().cpu().numpy() - ref).max()
+        assert err <= 2e-2 * np.abs(ref).max(), f"{err:.3e} of {np.abs(ref).max():.3e}"
+    run(None, None, None)
+    n_items, need, n_tickets = native.attention_prefill_tc_plan(sizes, heads, kv, hd, 0)
+    if n_items:
+        run(torch.empty(max(need, 16), dtype=torch.uint8, device="cuda"),
+            torch.zeros(max(n_tickets, 1), dtype=torch.int32, device="cuda"), sizes)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_heads_of_the_fast_kernels_through_the_engine(dtype):
+    """Heads of 64 and 128 with two query heads a key head: bfloat16 prompts take the tcgen05
+    prompt kernel chunk by chunk (the borrower over the lender's rows), single rows the decode
+    kernel; portions of several rows go row by row over the cache."""
+    cfg = model(96, 150, [attention(4, 2, 64, 64, 48, rot_dims=16, scale=0.3, mlp=dense(64)),
+                          attention(4, 2, 64, 64, 80, rot_dims=16, scale=0.3, kv_from=0),
+                          attention(2, 1, 128, 128, 0, scale=0.2),
+                          attention(4, 2, 64, 64, 200, rot_dims=16, scale=0.3, kv_from=0, mlp=dense(32))])
+    w = random_weights(cfg, seed=61)
+    eng = make_engine(cfg, w, dtype)
+    toks = prompts(cfg, [330], seed=62)[0]
+    ref = plain_logits(cfg, w, toks)
+    assert_close(run_whole(eng, toks), ref, dtype, "whole prompt")
+    assert_close(run_portions(eng, toks, [150, 2, 40, 48] + [1] * 90), ref, dtype, "portions and single tokens")
+    a, b = toks[:260], prompts(cfg, [120], seed=63)[0]
+    rb = plain_logits(cfg, w, b)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([(sa, a[:200]), (sb, b[:47])], [all_rows(200), all_rows(47)])
+    assert_close(out, torch.cat([ref[:200], rb[:47]]), dtype, "two prompts")
+    for k in range(60):
+        out = eng.step([(sa, [a[200 + k]]), (sb, [b[47 + k]])], [[0], [0]])
+        assert_close(out, torch.stack([ref[200 + k], rb[47 + k]]), dtype, f"two requests, token {k}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows, inter", [(1, 264), (8, 264), (12, 100), (130, 264), (300, 264), (300, 100), (40, 7)])
+def test_clipped_gated_feed_forward_alone(rows, inter, dtype):
+    """The dense feed-forward part alone at row counts that take the weight-streaming product with
+    the clipped epilogue, the library's product with the activation behind it, and the tensor-core
+    product with the epilogue; widths that are and are not multiples of 8; values beyond the limit."""
+    from strata_inference_b200.parts.base import Runtime, build_part
+    from strata_inference_b200.parts.feed_forward import ClippedGatedMLP
+    g = torch.Generator().manual_seed(rows + inter)
+    hidden = 128
+    stored = {"gate_proj.weight": torch.randn((inter, hidden), generator=g) * 0.25,
+              "up_proj.weight": torch.randn((inter, hidden), generator=g) * 0.25,
+              "down_proj.weight": torch.randn((hidden, inter), generator=g) * 0.2}
+    stored = {n: t.to(torch.bfloat16) for n, t in stored.items()}
+    rt = Runtime("cuda:0", dtype)
+    part = build_part(ClippedGatedMLP, ({"intermediate_size": inter, "limit": 1.5, "alpha": 1.702}, hidden),
+                      {n: t.cuda() for n, t in stored.items()}, rt)
+    x = torch.randn((rows, hidden), generator=g).to(torch.bfloat16)
+    got = part.forward(x.cuda().to(dtype), None).float().cpu().double().numpy()
+    w = {n.split("_")[0]: plain.f64(t.float()) for n, t in stored.items()}
+    assert (plain.f64(x.float()) @ w["gate"].T).max() > 1.5 and (plain.f64(x.float()) @ w["up"].T).min() < -1.5
+    ref = plain.clipped_gated_ff(plain.f64(x.float()), w, 1.5)
+    assert np.abs(got - ref).max() <= (1e-4 if dtype == torch.float32 else 2e-2) * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("rows, heads, vd", [(1, 1, 2048), (9, 1, 600), (5, 3, 512), (40, 1, 1000)])
+def test_norm_and_gate_over_many_columns(rows, heads, vd):
+    """Heads of 512 columns and more (all heads normed together count as one) take a block a
+    row: x / rms(x) * w * sigmoid(gate) against the plain formula."""
+    from strata_inference_b200.kernels import native
+    g = torch.Generator().manual_seed(vd)
+    o = torch.randn((rows, heads * vd), generator=g) * 3
+    w = torch.randn(heads * vd, generator=g)
+    gate = torch.randn((rows, heads * vd + 8), generator=g).to(torch.bfloat16)
+    y = torch.empty((rows, heads * vd), dtype=torch.bfloat16, device="cuda")
+    native.head_norm_gate(_dev(o), None, _dev(w), gate.cuda()[:, :heads * vd], y, heads, vd, 1e-5, native.GATE_SIGMOID)
+    x = o.double().numpy().reshape(rows, heads, vd)
+    want = plain.unit_rms(x, 1e-5) * w.double().numpy().reshape(heads, vd) * plain.sigmoid(
+        gate[:, :heads * vd].double().numpy().reshape(rows, heads, vd))
+    assert np.abs(y.float().cpu().numpy().reshape(rows, heads, vd) - want).max() <= 2e-2 * np.abs(want).max()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
