@@ -228,3 +228,46 @@ def decisive_routers(weights: Dict[str, torch.Tensor], factor: float = 6.0) -> D
     bfloat16 run chooses the experts the plain model chooses."""
     return {n: (t * factor).to(torch.bfloat16).to(torch.float32) if n.endswith(".router") else t
             for n, t in weights.items()}
+
+
+def random_model(seed: int) -> dict:
+    """A configuration drawn from the design's whole range: any order of the three mixers, borrowers
+    behind any lender, grouped and ungrouped heads of the fast kernels' widths and of others, values
+    wider and narrower than keys, chunks of any length or none, every kind of feed-forward or none."""
+    import random
+    r = random.Random(seed)
+    width, vocab = r.choice([64, 96, 128]), r.randrange(90, 300)
+
+    def mlp():
+        kind = r.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            return None
+        if kind == "dense":
+            return dense(r.choice([24, 40, 100, 128]), r.choice([0.8, 2.5, 6.0]))
+        experts = r.randrange(2, 10)
+        return moe(experts, r.randrange(1, min(experts, 4) + 1), r.choice([8, 24, 40]), r.choice([0, 0, 16, 36]))
+    layers, lenders = [], []
+    for i in range(r.randrange(3, 7)):
+        kind = r.choice(["attention", "attention", "latent", "lightning"])
+        if kind == "attention" and lenders and r.random() < 0.7:
+            j = r.choice(lenders)
+            m = layers[j]["mixer"]
+            layers.append(attention(m["heads"], m["kv_heads"], m["dim"], m["vdim"], r.choice([0, 5, 16, 37, 64, 100]),
+                                    scale=r.choice([0.1, 0.3]), rot_dims=m["rot"]["dims"] if m.get("rot") else 0,
+                                    base=m["rot"]["base"] if m.get("rot") else 10000.0, mlp=mlp(), kv_from=j))
+        elif kind == "attention":
+            kv = r.choice([1, 2, 4])
+            heads = kv * r.choice([1, 2, 4])
+            dim = r.choice([16, 32, 64, 64, 128, 24])
+            vdim = r.choice([dim, dim, dim, 16, 48, 128])
+            lenders.append(i)
+            layers.append(attention(heads, kv, dim, vdim, r.choice([0, 5, 16, 37, 64, 100]), scale=r.choice([0.1, 0.3]),
+                                    rot_dims=r.choice([0, 2, dim // 2, dim]), base=r.choice([10000.0, 500000.0]), mlp=mlp()))
+        elif kind == "latent":
+            layers.append(latent(r.randrange(1, 5), r.choice([8, 16, 32, 64]), r.choice([4, 8, 16, 32]), r.choice([8, 16, 40]),
+                                 r.choice([8, 24, 48, 100]), r.choice([8, 20, 64]), scale=r.choice([0.1, 0.3]), mlp=mlp()))
+        else:
+            heads = r.randrange(1, 5)
+            layers.append(lightning(heads, r.choice([8, 16, 32, 64]), r.choice([8, 16, 24, 64]),
+                                    [r.choice([0.5, 0.9, 0.97, 0.999, 1.0]) for _ in range(heads)], mlp=mlp()))
+    return model(width, vocab, layers, eps=r.choice([1e-5, 1e-6]), scale=r.choice([0.5, 1.0, 2.0]), mult=r.choice([0.3, 0.5, 1.0]))

@@ -18,7 +18,7 @@ import torch
 
 import plain_besorax as plain
 from besorax_cases import (ALONE, MIXED, ODD, SHARP, WIDE, assert_close, attention, changed, decisive_routers, dense,
-                           lightning, model, moe, plain_logits, prompts, random_weights, rows_that_differ)
+                           lightning, model, moe, plain_logits, prompts, random_model, random_weights, rows_that_differ)
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
@@ -325,6 +325,28 @@ def test_other_sizes(name, dtype):
     for k in range(10):
         out = eng.step([(sa, [a[140 + k]]), (sb, [b[50 + k]])], [[0], [0]])
         assert_close(out, torch.stack([ref[140 + k], rb[50 + k]]), dtype, f"{name}: two requests, token {k}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_configurations_drawn_at_random(seed, dtype):
+    """Any order of layers, any lender, any of the sizes: a prompt, portions down to two tokens with
+    single tokens behind them, and two unequal requests together."""
+    cfg = random_model(seed)
+    w = weights_for(cfg, 70 + seed, dtype)
+    eng = make_engine(cfg, w, dtype)
+    toks = prompts(cfg, [170], seed=seed)[0]
+    ref = plain_logits(cfg, w, toks)
+    assert_close(run_whole(eng, toks), ref, dtype, f"drawn model {seed}: whole prompt")
+    assert_close(run_portions(eng, toks, [70, 2, 30, 18] + [1] * 50), ref, dtype, f"drawn model {seed}: portions and tokens")
+    a, b = toks[:120], prompts(cfg, [60], seed=seed + 100)[0]
+    rb = plain_logits(cfg, w, b)
+    sa, sb = eng.new_sequence(), eng.new_sequence()
+    out = eng.step([(sa, a[:101]), (sb, b[:33])], [all_rows(101), all_rows(33)])
+    assert_close(out, torch.cat([ref[:101], rb[:33]]), dtype, f"drawn model {seed}: two prompts")
+    for k in range(19):
+        out = eng.step([(sa, [a[101 + k]]), (sb, [b[33 + k]])], [[0], [0]])
+        assert_close(out, torch.stack([ref[101 + k], rb[33 + k]]), dtype, f"drawn model {seed}: two requests, token {k}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
