@@ -25,7 +25,7 @@
 
 enum { GEMM_EPI_NONE = 0, GEMM_EPI_SOFTCAP = 1, GEMM_EPI_GEGLU = 2, GEMM_EPI_SWIGLU = 4,
        GEMM_EPI_RELU2 = 5,      // (5: the square of max(y, 0), value by value)
-       GEMM_EPI_CLIPPED = 6 };  // (6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
+       GEMM_EPI_CLIPPED = 6, GEMM_EPI_GELU = 7 };  // (7: the exact gelu, value by value; 6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
                                 //  u = clamp(u, -cap, cap); `cap` carries the limit)
 
 static constexpr int BM = 128;        // weight rows per block
@@ -244,6 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         float o = __uint_as_float(v[j]);
                         if (p.epilogue == GEMM_EPI_SOFTCAP) o = p.cap * tanhf(o / p.cap);
                         if (p.epilogue == GEMM_EPI_RELU2) { o = fmaxf(o, 0.f); o *= o; }
+                        if (p.epilogue == GEMM_EPI_GELU) o = 0.5f * o * (1.0f + erff(o * 0.70710678118654752f));
                         const int r = r0 + c0 + j;
                         if (n < p.N && r < p.R) y[(size_t)r * p.y_stride + n] = from_f32<OutT>(o);
                     }
@@ -518,6 +519,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         o[j] = __uint_as_float(v[j]);
                         if (p.epilogue == GEMM_EPI_SOFTCAP) o[j] = p.cap * tanhf(o[j] / p.cap);
                         if (p.epilogue == GEMM_EPI_RELU2) { o[j] = fmaxf(o[j], 0.f); o[j] *= o[j]; }
+                        if (p.epilogue == GEMM_EPI_GELU) o[j] = 0.5f * o[j] * (1.0f + erff(o[j] * 0.70710678118654752f));
                     }
                     store_run<OutT>(y + (size_t)r * p.y_stride + n, o, min(32, p.N - n));
                 }

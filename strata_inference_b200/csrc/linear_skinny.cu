@@ -35,7 +35,7 @@ namespace cg = cooperative_groups;
 
 enum { EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GEGLU = 2, EPI_ROPE = 3, EPI_SWIGLU = 4,
        EPI_RELU2 = 5,       // (5: the square of max(y, 0), value by value)
-       EPI_CLIPPED = 6 };   // (6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
+       EPI_CLIPPED = 6, EPI_GELU = 7 };   // (7: the exact gelu, value by value; 6: the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap),
                             //  u = clamp(u, -cap, cap); `cap` carries the limit)
 
 // What the q|k|v product needs to rotate and store (see rope_cache.cu for the cache layout).
@@ -286,6 +286,10 @@ __device__ __forceinline__ void skinny_linear_body(
 #pragma unroll
                 for (int c = 0; c < 4; ++c) { const float t = fmaxf(o[c], 0.f); o[c] = t * t; }
             }
+            if (EPI == EPI_GELU) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = 0.5f * o[c] * (1.0f + erff(o[c] * 0.70710678118654752f));
+            }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int n = n_lo + (c >= 2 ? 8 : 0), r = r0 + (c & 1);
@@ -426,6 +430,7 @@ SIB_EXPORT int sib_skinny_linear(const void* W, const void* x, void* y, int out_
         if (epilogue == EPI_SOFTCAP) GO(__nv_bfloat16, EPI_SOFTCAP);
         if (epilogue == EPI_RELU2) GO(__nv_bfloat16, EPI_RELU2);
         if (epilogue == EPI_CLIPPED) GO(__nv_bfloat16, EPI_CLIPPED);
+        if (epilogue == EPI_GELU) GO(__nv_bfloat16, EPI_GELU);
     } else if (out_dtype == SIB_F32) {
         if (epilogue == EPI_NONE) GO(float, EPI_NONE);
         if (epilogue == EPI_SOFTCAP) GO(float, EPI_SOFTCAP);

@@ -124,6 +124,35 @@ router_rows_kernel(const T* __restrict__ x, long long x_stride, const float* __r
 
 // `group` 8: gate and up columns lie interleaved in eights (8 gates, then their 8 ups), as the
 // products with a gated epilogue keep their matrices; 0: all gates, then all ups.
+// Few rows and many experts: the logits alone, a warp per (row, expert) and 4 experts a block, so
+// that the router's matrix is read by many blocks at once; router_topk_kernel then chooses.
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_logits_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ w,
+                     float* __restrict__ z, int width, int experts) {
+    extern __shared__ __align__(16) float xs[];      // [width] the row
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.y;
+    pdl_wait();
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32(x[(size_t)r * x_stride + c]);
+    __syncthreads();
+    const int e = blockIdx.x * 4 + warp;
+    if (e >= experts) return;
+    const float* row = w + (size_t)e * width;
+    float acc = 0.f;
+    if (width % 4 == 0 && ((uintptr_t)w % 16) == 0) {
+        for (int c = lane * 4; c < width; c += 128) {
+            const float4 a = *(const float4*)(row + c), b = *(const float4*)(xs + c);
+            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        }
+    } else {
+        for (int c = lane; c < width; c += 32) acc += row[c] * xs[c];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) z[(size_t)r * experts + e] = acc;
+}
+
 template <typename T>
 __global__ void expert_activate_kernel(const T* __restrict__ gu, long long stride, T* __restrict__ y,
                                        const float* __restrict__ row_weight, int ff, float limit,
@@ -477,10 +506,22 @@ SIB_EXPORT int sib_router_topk(const float* logits, const float* bias, int* ids,
 
 SIB_EXPORT int sib_router_rows(const void* x, long long x_stride, int dtype, const float* w,
                                const float* bias, int* ids, float* weights, int rows, int width,
-                               int experts, int top, int score, void* stream) {
+                               int experts, int top, int score, float* logits, void* stream) {
     if (rows == 0) return 0;
     SIB_REQUIRE(rows > 0 && width > 0 && experts > 0 && top > 0 && top <= experts && top <= 32,
                 "router_rows: rows=%d width=%d experts=%d top=%d", rows, width, experts, top);
+    if (logits != nullptr && experts >= 16 && rows < 65536 && (size_t)width * 4 <= 48 * 1024) {
+        // (one block a row walked 32 experts' rows of 2 048 in 23 us; spread over the device the
+        // product and the choice are two launches of a few us)
+        SIB_DISPATCH_DTYPE(dtype, sib_launch_chained(router_logits_kernel<T>, dim3((experts + 3) / 4, rows),
+                                                     dim3(128), (size_t)width * 4, (cudaStream_t)stream,
+                                                     (const T*)x, x_stride, w, logits, width, experts));
+        int rc = sib_check_launch("router_logits");
+        if (rc) return rc;
+        sib_launch_chained(router_topk_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
+                           (const float*)logits, bias, ids, weights, rows, experts, top, score);
+        return sib_check_launch("router_topk");
+    }
     const size_t shared = ((size_t)((width + 3) & ~3) + experts) * 4;
     SIB_REQUIRE(shared <= 48 * 1024, "router_rows: a row of %d and %d logits do not fit shared memory",
                 width, experts);

@@ -24,6 +24,7 @@ EPI_RELU2 = 5           # the square of max(y, 0), value by value (the same two 
 # the clipped gate, g sigmoid(1.702 g) (u + 1) with g = min(g, cap), u = clamp(u, -cap, cap): the
 # products' ``cap`` carries the limit (the same two products)
 EPI_CLIPPED = 6
+EPI_GELU = 7            # the exact (erf) gelu, value by value (the same two products)
 GATED_EPILOGUES = (EPI_GEGLU, EPI_SWIGLU, EPI_CLIPPED)
 ROPE_HALF_SPLIT, ROPE_INTERLEAVED = 0, 1
 ACT_GELU_TANH, ACT_SILU = 0, 1          # of the gated feed-forward
@@ -550,9 +551,11 @@ def router_rows(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
         _f32(bias, experts, "bias")
     if w.shape[1] != width or ids.shape[0] != rows or x.stride(1) != 1:
         raise KernelError("router_rows: shapes do not fit")
+    # (with 16 experts and more the logits are made by many blocks and left here for the choice)
+    logits = torch.empty((rows, experts), dtype=torch.float32, device=x.device) if experts >= 16 else None
     _check(library().sib_router_rows(_ptr(x), c_longlong(x.stride(0)), _code(x.dtype), _ptr(w), _ptr(bias),
                                      _ptr(ids), _ptr(weights), c_int(rows), c_int(width),
-                                     c_int(experts), c_int(top), c_int(score), _stream()))
+                                     c_int(experts), c_int(top), c_int(score), _ptr(logits), _stream()))
 
 
 @_timed(lambda gu, y, row_weight, limit, alpha, *a: ("expert_activate", _nbytes(gu, y), 0))

@@ -207,7 +207,7 @@ class Runtime:
         n_out = N // 2 if gated else N
         # (the chain kernel, the staged product and the tcgen05 weight-streaming product know
         # the tanh-GELU gate only)
-        only_gelu = epilogue not in (native.EPI_SWIGLU, native.EPI_RELU2, native.EPI_CLIPPED)
+        only_gelu = epilogue not in (native.EPI_SWIGLU, native.EPI_RELU2, native.EPI_CLIPPED, native.EPI_GELU)
         if self._chainable(x, w, out_dtype) and only_gelu and (out_dtype == torch.bfloat16
                                                                or not gated):
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
@@ -230,7 +230,7 @@ class Runtime:
             # the weight-streaming tcgen05 product, with its epilogue
             out = torch.empty((R, n_out), dtype=out_dtype, device=x.device)
             return native.linear_rows_tc(x, w, out, epilogue, cap)
-        fused_gate = (gated or (epilogue == native.EPI_RELU2 and self.fuse_relu2_gemm)) \
+        fused_gate = (gated or (epilogue in (native.EPI_RELU2, native.EPI_GELU) and self.fuse_relu2_gemm)) \
             and R > self.gated_gemm_min_rows
         if x.dtype == torch.bfloat16 and aligned and (out_dtype == torch.float32 or fused_gate):
             # the tcgen05 product where its epilogue saves a pass over the outputs: 32-bit
@@ -253,6 +253,8 @@ class Runtime:
             native.softcap_(y, cap)
         elif epilogue == native.EPI_RELU2:
             native.activate(y, y, native.ACT_RELU_SQUARED)
+        elif epilogue == native.EPI_GELU:
+            native.expert_activate(y, y, None, 0.0, 0.0, native.FORM_PLAIN_GELU)
         return y
 
 

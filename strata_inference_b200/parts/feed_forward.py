@@ -319,13 +319,18 @@ class RoutedExperts:
         rt.flush()
         ids, p = self.choose(x)
         base: Optional[torch.Tensor] = None
-        if self.sff:
+        if self.sff and self.plain:
+            # (the gelu is an epilogue of the up product where a hand-written product runs)
+            base = rt.linear(rt.linear(x, self.w_sgu, epilogue=native.EPI_GELU), self.w_sdown)
+        elif self.sff:
             gu = rt.linear(x, self.w_sgu)
             mid = torch.empty((R, self.sff), dtype=x.dtype, device=x.device)
             native.expert_activate(gu, mid, None, self.shared_limit, self.alpha, self.form)
             base = rt.linear(mid, self.w_sdown)
         out = torch.empty((R, self.hidden), dtype=x.dtype, device=x.device)
-        if R <= self.pair_rows:
+        # (the streamed kernels keep a row and its `top` middles in shared memory)
+        streams = self.hidden * 4 <= 48 * 1024 and self.top * self.ff * 4 <= 48 * 1024
+        if R <= self.pair_rows and streams and R * self.top < 65536:
             return native.routed_rows(x, self.w_gu, self.w_down, ids, p, base, out, self.limit, self.alpha,
                                       self.form)
         # The pairs sorted by expert and laid out [experts, most, width] with `most` the largest

@@ -236,7 +236,7 @@ def random_model(seed: int) -> dict:
     wider and narrower than keys, chunks of any length or none, every kind of feed-forward or none."""
     import random
     r = random.Random(seed)
-    width, vocab = r.choice([64, 96, 128]), r.randrange(90, 300)
+    width, vocab = r.choice([64, 96, 128, 100, 36]), r.randrange(90, 300)
 
     def mlp():
         kind = r.choice(["none", "dense", "moe", "moe"])

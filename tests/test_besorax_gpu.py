@@ -404,6 +404,25 @@ def test_router_scores_are_sigmoids_of_the_chosen(rows, experts, top):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows, width, experts, top", [(1, 64, 8, 2), (5, 100, 16, 3), (8, 256, 40, 4), (32, 72, 33, 1)])
+def test_router_of_few_rows(rows, width, experts, top, dtype):
+    """The router's 32-bit product and the choice in one call, with few and with many experts (the
+    logits of 16 and more are made by many blocks): ids and sigmoid scores against the plain sort."""
+    from strata_inference_b200.kernels import native
+    g = torch.Generator().manual_seed(rows + experts)
+    x = torch.randn((rows, width), generator=g).to(dtype).float()
+    w = torch.randn((experts, width), generator=g) * 0.3
+    ids = torch.empty((rows, top), dtype=torch.int32, device="cuda")
+    p = torch.empty((rows, top), dtype=torch.float32, device="cuda")
+    native.router_rows(_dev(x, dtype), _dev(w), None, ids, p, native.SCORE_SIGMOID)
+    s = plain.sigmoid(x.double().numpy() @ w.double().numpy().T)
+    for r in range(rows):
+        want = np.argsort(-s[r], kind="stable")[:top]
+        assert ids[r].tolist() == want.tolist()
+        assert np.allclose(p[r].cpu().numpy(), s[r][want], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows, width, ff, experts, top", [(1, 64, 24, 4, 1), (3, 72, 10, 5, 2), (20, 128, 97, 6, 3),
                                                           (32, 256, 64, 40, 4)])
 def test_streamed_experts_without_a_gate(rows, width, ff, experts, top, dtype):
