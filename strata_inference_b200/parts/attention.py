@@ -68,7 +68,7 @@ kernel, whose first key is the start of the row's chunk and whose joins add the 
 everything else (32-bit, shapes those two do not take, recorded prompt steps) the general
 kernel.
 
-Worked-on heads (any of the options above ``chunk``) are rotated in half-split or neighbouring pairs,
+Worked-on heads (any of the options from ``value_dim`` to ``pool``) are rotated in half-split or neighbouring pairs,
 as the position part says, and are attended to by the general kernel when a window is set.
 """
 
