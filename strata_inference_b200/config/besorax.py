@@ -35,6 +35,7 @@ the same form sees every token.  The logits have a matrix of their own.  Tensor 
 
 from __future__ import annotations
 
+import copy
 from dataclasses import dataclass
 from typing import Any, Dict, List, Mapping, Optional, Tuple
 
@@ -202,6 +203,71 @@ class BesoraxConfig:
 
     def to_dict(self) -> dict:
         return dict(self.raw)
+
+
+def besorax_sizes(config: Mapping[str, Any], shapes: Mapping[str, Tuple[int, ...]]) -> dict:
+    """config.json completed with the sizes that it leaves to a folder's tensors: a size that
+    config.json gives stays as it is; one that it omits is read off the shape of the tensor that
+    has it (head counts cannot be, and stay required)."""
+    out = copy.deepcopy(dict(config))
+
+    def rows(name):
+        shape = shapes.get(name)
+        return int(shape[0]) if shape else None
+
+    def cols(name):
+        shape = shapes.get(name)
+        return int(shape[1]) if shape and len(shape) == 2 else None
+
+    def fill(d, key, value):
+        if isinstance(d, dict) and d.get(key) is None and value:
+            d[key] = int(value)
+    fill(out, "vocab", rows("embed"))
+    fill(out, "width", cols("embed"))
+    for i, l in enumerate(out.get("layers") or []):
+        m = l.get("mixer") if isinstance(l, dict) else None
+        if not isinstance(m, dict) or not isinstance(m.get("heads"), int) or m["heads"] <= 0:
+            continue
+        H, pre = m["heads"], f"l{i}.mix."
+        if l.get("type") == "attention":
+            fill(m, "dim", (rows(pre + "q") or 0) // H)
+            fill(m, "vdim", (cols(pre + "o") or 0) // H)
+            if m.get("kv_from") is None and m.get("dim"):
+                fill(m, "kv_heads", (rows(pre + "k") or 0) // m["dim"])
+        elif l.get("type") == "latent_attention":
+            fill(m, "q_rank", rows(pre + "dq"))
+            fill(m, "kv_rank", rows(pre + "dkv.norm"))
+            if m.get("kv_rank"):
+                fill(m, "rot_dim", (rows(pre + "dkv") or 0) - m["kv_rank"])
+            fill(m, "dim", (rows(pre + "uk") or 0) // H)
+            fill(m, "vdim", (rows(pre + "uv") or 0) // H)
+        elif l.get("type") == "lightning":
+            fill(m, "dim", (rows(pre + "q") or 0) // H)
+            fill(m, "vdim", (rows(pre + "v") or 0) // H)
+        mlp, pre = l.get("mlp"), f"l{i}.mlp."
+        if not isinstance(mlp, dict):
+            continue
+        if mlp.get("kind", "dense") == "dense":
+            fill(mlp, "ff", rows(pre + "gate"))
+        else:
+            mlp.setdefault("router", {})
+            mlp.setdefault("expert", {})
+            fill(mlp["router"], "experts", rows(pre + "router"))
+            fill(mlp["expert"], "ff", rows(pre + "e0.up"))
+            if mlp.get("shared") is None and rows(pre + "shared.up"):
+                mlp["shared"] = {}
+            if isinstance(mlp.get("shared"), dict):
+                fill(mlp["shared"], "ff", rows(pre + "shared.up"))
+    # (a layer that reads another's keys and values has no tensor that says how many key heads there are)
+    layers = out.get("layers") or []
+    for l in layers:
+        m = l.get("mixer") if isinstance(l, dict) else None
+        src = m.get("kv_from") if isinstance(m, dict) else None
+        if isinstance(src, int) and not isinstance(src, bool) and 0 <= src < len(layers):
+            lender = layers[src].get("mixer") if isinstance(layers[src], dict) else None
+            if isinstance(lender, dict):
+                fill(m, "kv_heads", lender.get("kv_heads"))
+    return out
 
 
 _NORM_NAMES = {"weight": "", "b": ".b", "alpha": ".alpha"}

@@ -91,8 +91,8 @@ def _register_builtin() -> None:
     register_architecture(("Vavupel", "vavupel"), VavupelConfig.from_dict, vavupel_spec)
     from .gegorax import GegoraxConfig, gegorax_sizes, gegorax_spec
     register_architecture(("Gegorax", "gegorax"), GegoraxConfig.from_dict, gegorax_spec, gegorax_sizes)
-    from .besorax import BesoraxConfig, besorax_spec
-    register_architecture(("Besorax", "besorax"), BesoraxConfig.from_dict, besorax_spec)
+    from .besorax import BesoraxConfig, besorax_sizes, besorax_spec
+    register_architecture(("Besorax", "besorax"), BesoraxConfig.from_dict, besorax_spec, besorax_sizes)
 
 
 _register_builtin()

@@ -216,3 +216,27 @@ def test_plain_layer_scales_what_it_adds():
     h = plain.dynamic_tanh(x1, plain.f64(w["l0.norm2"]), plain.f64(w["l0.norm2.b"]), float(w["l0.norm2.alpha"]))
     x2 = x1 + 0.25 * plain.clipped_gated_ff(h, plain.sub(w, "l0.mlp."), 2.5)
     assert np.allclose(plain.layer_streams(cfg, w, toks)[0], x2)
+
+
+def test_sizes_that_the_configuration_omits_come_from_the_tensors():
+    """A folder's config.json may leave a size to the tensors' shapes: the completed configuration is
+    the full one; a size that is given stays as given."""
+    from strata_inference_b200.config.besorax import besorax_sizes
+    for cfg in (MIXED, ODD):
+        shapes = {n: tuple(t.shape) for n, t in random_weights(cfg, seed=1).items()}
+        bare = copy.deepcopy(cfg)
+        del bare["vocab"], bare["width"]
+        for layer in bare["layers"]:
+            m = layer["mixer"]
+            for key in ("dim", "vdim", "kv_heads", "q_rank", "kv_rank", "rot_dim"):
+                m.pop(key, None)
+            if layer["mlp"]:
+                layer["mlp"].pop("ff", None)
+                layer["mlp"].get("router", {}).pop("experts", None)
+                layer["mlp"].get("expert", {}).pop("ff", None)
+                if layer["mlp"].get("shared"):
+                    layer["mlp"]["shared"].pop("ff")
+        full = besorax_sizes(bare, shapes)
+        assert spec_from_config(full)[1] == spec_from_config(cfg)[1]
+        assert spec_from_config(bare, shapes)[1] == spec_from_config(cfg)[1]
+        assert besorax_sizes(cfg, shapes) == cfg
